@@ -5,7 +5,8 @@ from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .llama import LlamaConfig
 from .dunelix import DunelixConfig
 from .zozenex import ZozenexConfig
+from .fiponex import FiponexConfig
 
-__all__ = ["ConfigError", "LlamaConfig", "DunelixConfig", "ZozenexConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
+__all__ = ["ConfigError", "LlamaConfig", "DunelixConfig", "ZozenexConfig", "FiponexConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
            "config_class_for", "config_from_dict", "load_config", "register_architecture",
            "registered_architectures"]

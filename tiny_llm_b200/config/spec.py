@@ -76,3 +76,5 @@ class ModelSpec:
     on_logits: Optional[PartSpec] = None
     after_embedding_name: str = "model.after_embedding"
     on_logits_name: str = "model.on_logits"
+    # the embedding rows are multiplied by this (in 32-bit, as they are gathered into the stream)
+    embedding_scale: float = 1.0

@@ -127,11 +127,12 @@ __device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int
 
 // The merge of the eight softmaxes, way 0 first: `m`, `l`, `o` of way w are read through the three functions.
 template <int OD, typename FM, typename FL, typename FO>
-__device__ __forceinline__ void merge_ways(FM way_m, FL way_l, FO way_o, float* o_out, float& l_out) {
+__device__ __forceinline__ void merge_ways(FM way_m, FL way_l, FO way_o, float* o_out, float& l_out, float& m_out) {
   float mx = -CUDART_INF_F;
 #pragma unroll
   for (int w = 0; w < WAYS; ++w) mx = fmaxf(mx, way_m(w));
   const float m_ref = mx == -CUDART_INF_F ? 0.f : mx;
+  m_out = m_ref;
   l_out = 0.f;
 #pragma unroll
   for (int i = 0; i < OD; ++i) o_out[i] = 0.f;
@@ -142,6 +143,16 @@ __device__ __forceinline__ void merge_ways(FM way_m, FL way_l, FO way_o, float* 
 #pragma unroll
     for (int i = 0; i < OD; ++i) o_out[i] = fmaf(way_o(w, i), f, o_out[i]);
   }
+}
+
+// What the merged sums are multiplied by: 1 / l, or, with a sink (a learned score per head that joins the softmax's
+// denominator and has no value), 1 / (l + exp(sink - m)) with both terms taken against the larger of m and the sink.
+__device__ __forceinline__ float inverse_sum(float l, float m, const float* sink, int head) {
+  if (sink == nullptr) return 1.f / l;
+  const float sk = sink[head];
+  const float top = fmaxf(m, sk);
+  const float f = expf(m - top);
+  return f / fmaf(l, f, expf(sk - top));
 }
 
 // The same tile for up to GH query heads that share the key/value head: every key row and value row is fetched once
@@ -242,7 +253,7 @@ paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const 
                                const T* __restrict__ vcache, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ token_request,
                                const int* __restrict__ positions, TO* __restrict__ out, int n_tokens,
-                               Geometry g, float scale) {
+                               Geometry g, float scale, const float* __restrict__ sink) {
   constexpr int GW = GroupedWarps<OD>::N;
   __shared__ __align__(16) float q_s[GW][GH][OD * 32];
   __shared__ float way_s[GW][WAYS][GH][OD * 32 + 2];
@@ -290,11 +301,11 @@ paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const 
   }
   __syncwarp();
   for (int i = 0; i < nh; ++i) {
-    float o[OD], l;
+    float o[OD], l, mx;
     merge_ways<OD>([&](int w) { return way_s[warp][w][i][OD * 32]; }, [&](int w) { return way_s[warp][w][i][OD * 32 + 1]; },
-                   [&](int w, int x) { return way_s[warp][w][i][lane + 32 * x]; }, o, l);
+                   [&](int w, int x) { return way_s[warp][w][i][lane + 32 * x]; }, o, l, mx);
     TO* orow = out + (size_t)t * nq * vd + (size_t)((kvh * group + h0 + i) * maps + map) * vd;
-    const float inv = 1.f / l;
+    const float inv = inverse_sum(l, mx, sink, kvh * group + h0 + i);
 #pragma unroll
     for (int x = 0; x < OD; ++x) {
       const int d = lane + 32 * x;
@@ -311,7 +322,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
                                const T* __restrict__ vcache, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ token_request,
                                const int* __restrict__ positions, TO* __restrict__ out, int n_tokens,
-                               Geometry g, float scale) {
+                               Geometry g, float scale, const float* __restrict__ sink) {
   __shared__ __align__(16) float q_s[SPLIT ? 1 : WARPS][MAX_HD];
   __shared__ float merge_s[SPLIT ? WAYS : 1][SPLIT ? OD * 32 + 2 : 1];
   pdl_trigger();
@@ -339,7 +350,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
   }
 
   const int first_group = (lo / (32 * WAYS)) * (32 * WAYS);   // tile numbers are absolute: way = (j0 / 32) % WAYS
-  float o[OD], l;
+  float o[OD], l, mx;
   if (SPLIT) {
     Softmax<OD> st;
     st.m = -CUDART_INF_F; st.l = 0.f;
@@ -355,7 +366,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
     __syncthreads();
     if (warp != 0) return;
     merge_ways<OD>([&](int w) { return merge_s[w][OD * 32]; }, [&](int w) { return merge_s[w][OD * 32 + 1]; },
-               [&](int w, int i) { return lane + 32 * i < vd ? merge_s[w][lane + 32 * i] : 0.f; }, o, l);
+               [&](int w, int i) { return lane + 32 * i < vd ? merge_s[w][lane + 32 * i] : 0.f; }, o, l, mx);
   } else {
     Softmax<OD> st[WAYS];
 #pragma unroll
@@ -372,10 +383,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
           attend_tile(st[w], j0, lo, p, q_row, kcache, vcache, table, max_blocks, kh, vh, g, lane);
       }
     }
-    merge_ways<OD>([&](int w) { return st[w].m; }, [&](int w) { return st[w].l; }, [&](int w, int i) { return st[w].o[i]; }, o, l);
+    merge_ways<OD>([&](int w) { return st[w].m; }, [&](int w) { return st[w].l; }, [&](int w, int i) { return st[w].o[i]; }, o, l, mx);
   }
   TO* orow = out + (size_t)t * nq * vd + (size_t)h * vd;
-  const float inv = 1.f / l;
+  const float inv = inverse_sum(l, mx, sink, h / maps);
 #pragma unroll
   for (int i = 0; i < OD; ++i) {
     const int d = lane + 32 * i;
@@ -386,16 +397,16 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
 template <typename T, typename TO>
 static int launch_attention(const void* q, int q_row_stride, const void* kcache, const void* vcache, const int* block_table,
                             int max_blocks, const int* token_request, const int* positions, void* out, int n_tokens,
-                            const Geometry& g, float scale, bool split, bool grouped, int od, long long blocks,
-                            cudaStream_t s) {
+                            const Geometry& g, float scale, const float* sink, bool split, bool grouped, int od,
+                            long long blocks, cudaStream_t s) {
 #define TLLM_ATT_GENERIC(SPLIT_, OD_)                                                                                  \
   TLLM_LAUNCH("paged_attention_generic", (paged_attention_generic_kernel<T, TO, SPLIT_, OD_>), (unsigned)blocks,       \
               (SPLIT_ ? WAYS : WARPS) * 32, 0, s, (const T*)q, q_row_stride, (const T*)kcache, (const T*)vcache,       \
-              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale)
+              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale, sink)
 #define TLLM_ATT_GROUPED(OD_)                                                                                          \
   TLLM_LAUNCH("paged_attention_grouped", (paged_attention_grouped_kernel<T, TO, OD_>), (unsigned)blocks,               \
               GroupedWarps<OD_>::N * 32, 0, s, (const T*)q, q_row_stride, (const T*)kcache, (const T*)vcache,          \
-              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale)
+              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale, sink)
   if (split) {
     if (od == 2) TLLM_ATT_GENERIC(true, 2); else if (od == 4) TLLM_ATT_GENERIC(true, 4); else TLLM_ATT_GENERIC(true, 8);
   } else if (grouped) {
@@ -415,12 +426,14 @@ using namespace tllm;
 // Attention with `maps` score maps per head and key rows of `kd`, value rows of `vd` values.  `nq` query heads and
 // `nkv` key/value heads; the key cache holds nkv * maps rows per slot, the value cache nkv.  `chunk` > 0: keys are
 // visible inside the query's chunk of positions only.  out_f32 != 0: the output rows are float32 whatever the cache's type.
+// `sink` (float32, one per query head, or null): exp(sink) joins every softmax's denominator of that head.
 extern "C" int tllm_paged_attention_maps(const void* q, int q_row_stride, const void* kcache, const void* vcache,
                                          const int* block_table, int max_blocks, const int* token_request,
                                          const int* positions, void* out, int n_tokens, int nq, int nkv, int maps, int kd,
                                          int vd, int page_size, long long k_page_stride, long long k_head_stride,
                                          long long v_page_stride, long long v_head_stride, float scale, int window,
-                                         int chunk, int dtype, int out_f32, int split_override, void* stream) {
+                                         int chunk, int dtype, int out_f32, int split_override, const float* sink,
+                                         void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && maps > 0,
                "attention: %d tokens, %d heads, %d key/value heads (heads must be a multiple of key/value heads)", n_tokens, nq, nkv);
   TLLM_REQUIRE(kd >= 1 && kd <= MAX_HD && vd >= 1 && vd <= MAX_HD,
@@ -451,12 +464,12 @@ extern "C" int tllm_paged_attention_maps(const void* q, int q_row_stride, const 
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)
     return launch_attention<float, float>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request, positions, out,
-                                          n_tokens, g, scale, split, grouped, od, blocks, s);
+                                          n_tokens, g, scale, sink, split, grouped, od, blocks, s);
   if (out_f32)
     return launch_attention<__nv_bfloat16, float>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request,
-                                                  positions, out, n_tokens, g, scale, split, grouped, od, blocks, s);
+                                                  positions, out, n_tokens, g, scale, sink, split, grouped, od, blocks, s);
   return launch_attention<__nv_bfloat16, __nv_bfloat16>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request,
-                                                        positions, out, n_tokens, g, scale, split, grouped, od, blocks, s);
+                                                        positions, out, n_tokens, g, scale, sink, split, grouped, od, blocks, s);
 }
 
 extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, const void* kcache, const void* vcache,
@@ -471,5 +484,5 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
                "attention: cache rows must be 16-byte aligned");
   return tllm_paged_attention_maps(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request, positions, out,
                                    n_tokens, nq, nkv, 1, hd, hd, page_size, page_stride, head_stride, page_stride, head_stride,
-                                   scale, window, 0, dtype, 0, split_override, stream);
+                                   scale, window, 0, dtype, 0, split_override, nullptr, stream);
 }

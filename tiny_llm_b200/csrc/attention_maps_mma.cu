@@ -14,6 +14,8 @@
 // 32-bit rounding of the sums themselves) where a single bfloat16 operand would keep 8.  The output rows are float32
 // [token][head][map][VD], for the kernel that combines a head's maps.
 //
+// With a sink (a learned score per head) the softmax's denominator also holds exp(sink); it has no value row.
+//
 // Visibility: key j is visible to the row of a token at position p iff j <= p, j > p - window when there is a
 // window, and j >= (p / chunk) * chunk when keys are visible inside a chunk of positions only.
 #include "attention_tiles.cuh"
@@ -40,6 +42,7 @@ struct MapsParams {
   const int* cu_q;               // [R + 1]
   const int* q_start;            // [R]: position of the request's first token in this step
   float* out;                    // [T, nq * maps, VD]
+  const float* sink;             // [nq] or null: exp(sink) joins the denominator of every softmax of the head
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
   int q_row_stride, max_blocks, nq, nkv, maps, page_size, window, chunk, tiles_per_req, n_requests;
   float scale_log2;              // scale * log2(e)
@@ -274,7 +277,12 @@ attention_maps_kernel(const MapsParams p) {
   for (int half = 0; half < 2; ++half) {
     const int row = half ? r_b : r_a;
     if (row >= rows_total) continue;
-    const float inv = 1.f / (half ? l_b : l_a);
+    float inv = 1.f / (half ? l_b : l_a);
+    if (p.sink != nullptr) {   // both terms of the denominator against the larger of the running maximum and the sink
+      const float sk = p.sink[kvh * group + row % group] * 1.4426950408889634f, m = half ? m_b : m_a;
+      const float top = fmaxf(m, sk), f = ex2(m - top);
+      inv = f / fmaf(half ? l_b : l_a, f, ex2(sk - top));
+    }
     float* dst = p.out + ((size_t)(tok0 + row / group) * p.nq * p.maps + (size_t)((kvh * group + row % group) * p.maps + map)) * VD;
 #pragma unroll
     for (int i = 0; i < VD / 8; ++i)
@@ -291,7 +299,7 @@ extern "C" int tllm_attention_maps_mma(const void* q, int q_row_stride, const vo
                                        float* out, int n_tokens, int n_requests, int max_q_len, int nq, int nkv, int maps,
                                        int kd, int vd, int page_size, long long k_page_stride, long long k_head_stride,
                                        long long v_page_stride, long long v_head_stride, float scale, int window, int chunk,
-                                       void* stream) {
+                                       const float* sink, void* stream) {
   TLLM_REQUIRE(kd == KD && vd == VD, "attention_maps_mma: built for key size %d and value size %d, called with %d and %d", KD, VD, kd, vd);
   TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && maps > 0,
                "attention_maps_mma: %d tokens, %d requests, %d heads, %d key/value heads, %d maps", n_tokens, n_requests, nq, nkv, maps);
@@ -303,7 +311,7 @@ extern "C" int tllm_attention_maps_mma(const void* q, int q_row_stride, const vo
   const int group = nq / nkv;
   MapsParams p;
   p.q = (const __nv_bfloat16*)q; p.kcache = (const __nv_bfloat16*)kcache; p.vcache = (const __nv_bfloat16*)vcache;
-  p.block_table = block_table; p.cu_q = cu_q; p.q_start = q_start; p.out = out;
+  p.block_table = block_table; p.cu_q = cu_q; p.q_start = q_start; p.out = out; p.sink = sink;
   p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;
   p.q_row_stride = q_row_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.maps = maps; p.page_size = page_size;
   p.window = window; p.chunk = chunk; p.n_requests = n_requests;

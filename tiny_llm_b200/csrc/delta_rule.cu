@@ -1,0 +1,285 @@
+// The gated delta rule: a matrix state per head that is decayed, corrected towards the current value and read out,
+//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q            S: [key size, value size]
+// with q and k unit vectors per head (q also times a constant), one decay g and one step size beta per head and
+// token.  q, k and v come from short causal convolutions (one filter per channel) with SiLU behind them; the last
+// taps - 1 inputs of every channel are part of the request's state, beside S.  Decays, step sizes, unit norms, the
+// recurrence and the state are 32-bit; the projections are of the engine's dtype.
+//
+// delta_prepare: one warp per (token, head row).  The channels of the fused projection's row are
+//   [kvh heads of queries | kvh heads of keys | heads of values | ...]; a row's channels are filtered over the
+//   request's earlier tokens in this step and, ahead of them, the inputs kept in the state; SiLU; query and key rows
+//   are divided by sqrt(sum(x^2) + unit_eps); the value rows' warps also leave the head's decay and step size:
+//   g = exp(-exp(A_log) softplus(a + dt_bias)), beta = sigmoid(b).  All outputs float32.
+// conv_state_update: the state's kept inputs after the step: the last taps - 1 of (kept inputs ++ the step's).
+// delta_rule_scan: a group of 8 lanes owns one value column of one (request, head): the column's state rows lie in
+//   the lanes' registers (row = i * 8 + lane of the group).  Per token one round of shuffles gives the column's
+//   S^T k, S^T q and k . q from the state as it was; with those
+//       u = beta (v - g S^T k),   o = g S^T q + u (k . q),   S <- g S + k u
+//   which is the sequence above with the read-out written in terms of the old state.  Tokens are staged in shared
+//   memory eight at a time by cp.async, the next eight in flight meanwhile.  The state is kept transposed
+//   ([slot, head, value column, key row]) so that a group's rows are consecutive in memory.  What is done to a state
+//   element is the same sequence of operations however the request was cut into steps: the same bits.
+#include "common.cuh"
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float silu_exact(float x) { return x / (1.f + expf(-x)); }
+
+struct PrepArgs {
+  const void* proj;            // [T, ld]: channels first, then whatever else the projection carries
+  int ld;
+  const float* taps;           // [channels, n_taps]: the last column meets the current token
+  int n_taps;
+  const float* kept;           // [slots, n_taps - 1, channels]: inputs of the tokens before this step, oldest first
+  const int* slots;
+  const int* cu_q;
+  const int* token_request;
+  int heads, kv_heads, kd, vd;
+  int beta_col, a_col;         // columns of the projection row that hold b and a (one per head each)
+  const float* a_log;          // [heads]
+  const float* dt_bias;        // [heads]
+  float q_scale, unit_eps;
+  float *q, *k, *v, *gb;       // [T, kv_heads * kd] x 2, [T, heads * vd], [T, heads, 2] = (decay, step size)
+  int n_tokens;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prepare_kernel(PrepArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const int units = 2 * a.kv_heads + a.heads;
+  const long long task = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (task >= (long long)a.n_tokens * units) return;
+  const int lane = threadIdx.x & 31;
+  const int t = (int)(task / units), u = (int)(task % units);
+  const int req = a.token_request[t];
+  const int first = a.cu_q[req];
+  const int channels = 2 * a.kv_heads * a.kd + a.heads * a.vd;
+  const float* kept = a.kept + (size_t)a.slots[req] * (a.n_taps - 1) * channels;
+  const T* proj = (const T*)a.proj;
+  int c0, size;
+  float* dst;
+  const bool is_v = u >= 2 * a.kv_heads;
+  if (!is_v) {
+    c0 = u * a.kd; size = a.kd;
+    dst = (u < a.kv_heads ? a.q + (size_t)t * a.kv_heads * a.kd + (size_t)u * a.kd
+                          : a.k + (size_t)t * a.kv_heads * a.kd + (size_t)(u - a.kv_heads) * a.kd);
+  } else {
+    const int h = u - 2 * a.kv_heads;
+    c0 = 2 * a.kv_heads * a.kd + h * a.vd; size = a.vd;
+    dst = a.v + (size_t)t * a.heads * a.vd + (size_t)h * a.vd;
+  }
+  float ss = 0.f;
+  for (int d = lane; d < size; d += 32) {
+    const int c = c0 + d;
+    float y = 0.f;
+    for (int j = 0; j < a.n_taps; ++j) {
+      const int n = t - first - (a.n_taps - 1) + j;   // index among the request's tokens of this step; < 0: kept ones
+      const float x = n >= 0 ? to_f32(proj[(size_t)(first + n) * a.ld + c])
+                             : kept[(size_t)(a.n_taps - 1 + n) * channels + c];
+      y = fmaf(a.taps[(size_t)c * a.n_taps + j], x, y);
+    }
+    y = silu_exact(y);
+    dst[d] = y;
+    ss = fmaf(y, y, ss);
+  }
+  if (!is_v) {
+    ss = warp_sum(ss);
+    const float f = (u < a.kv_heads ? a.q_scale : 1.f) / sqrtf(ss + a.unit_eps);
+    __syncwarp();
+    for (int d = lane; d < size; d += 32) dst[d] = __fmul_rn(dst[d], f);
+  } else if (lane == 0) {
+    const int h = u - 2 * a.kv_heads;
+    const float za = to_f32(proj[(size_t)t * a.ld + a.a_col + h]) + a.dt_bias[h];
+    const float zb = to_f32(proj[(size_t)t * a.ld + a.beta_col + h]);
+    a.gb[((size_t)t * a.heads + h) * 2] = expf(-expf(a.a_log[h]) * softplus_f(za));
+    a.gb[((size_t)t * a.heads + h) * 2 + 1] = 1.f / (1.f + expf(-zb));
+  }
+}
+
+// One thread per (request, channel): kept[j] <- input at (the request's tokens after this step) - (n_taps - 1) + j.
+// Ascending j reads only entries at or above the one it writes, so the update is done in place.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ kept_all,
+                                         const int* __restrict__ slots, const int* __restrict__ cu_q, int n_taps,
+                                         int channels, int n_requests) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int req = blockIdx.y;
+  if (c >= channels || req >= n_requests) return;
+  const int first = cu_q[req], n = cu_q[req + 1] - first;
+  float* kept = kept_all + (size_t)slots[req] * (n_taps - 1) * channels;
+  for (int j = 0; j < n_taps - 1; ++j) {
+    const int i = n - (n_taps - 1) + j;   // index among this step's tokens; < 0: an input kept before
+    kept[(size_t)j * channels + c] = i >= 0 ? to_f32(proj[(size_t)(first + i) * ld + c]) : kept[(size_t)(j + n) * channels + c];
+  }
+}
+
+constexpr int DR_LANES = 8;            // lanes that share a value column
+constexpr int DR_COLS = 16;            // value columns per CTA of 128 threads
+constexpr int DR_TOK = 8;              // tokens staged at once
+
+struct ScanArgs {
+  const float *q, *k, *v, *gb;   // as delta_prepare leaves them
+  float* state;                  // [slots, heads, vd, kd]
+  const int* slots;
+  const int* cu_q;
+  float* out;                    // [T, heads * vd]
+  int heads, kv_heads, kd, vd;
+};
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int R>   // state rows per lane: R * DR_LANES >= key size
+__global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
+  constexpr int KP = R * DR_LANES;
+  // per stage: q and k of DR_TOK tokens (rows past the key size stay zero), their values of this CTA's columns,
+  // decay and step size
+  __shared__ float sq[2][DR_TOK][KP], sk[2][DR_TOK][KP], sv[2][DR_TOK][DR_COLS], sg[2][DR_TOK][2];
+  pdl_trigger();
+  const int tid = threadIdx.x;
+  const int sub = tid & (DR_LANES - 1), cl = tid / DR_LANES;
+  const int h = blockIdx.y, req = blockIdx.z;
+  const int col = blockIdx.x * DR_COLS + cl;
+  const bool col_ok = col < a.vd;
+  const int kh = h / (a.heads / a.kv_heads);
+  for (int i = tid; i < 2 * DR_TOK * KP; i += 128) { (&sq[0][0][0])[i] = 0.f; (&sk[0][0][0])[i] = 0.f; }
+  for (int i = tid; i < 2 * DR_TOK * DR_COLS; i += 128) (&sv[0][0][0])[i] = 0.f;
+  pdl_wait();
+  const int t0 = a.cu_q[req], t1 = a.cu_q[req + 1];
+  float* st = a.state + (((size_t)a.slots[req] * a.heads + h) * a.vd + (col_ok ? col : 0)) * a.kd;
+  float s[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int row = i * DR_LANES + sub;
+    s[i] = (col_ok && row < a.kd) ? st[row] : 0.f;
+  }
+  __syncthreads();   // the zeros are in place before any copy lands beside them
+  const int qk_ld = a.kv_heads * a.kd, v_ld = a.heads * a.vd;
+  auto stage = [&](int buf, int tb) {
+    const int nt = min(DR_TOK, t1 - tb);
+    for (int i = tid; i < nt * a.kd; i += 128) {
+      const int tt = i / a.kd, d = i % a.kd;
+      cp_async4(&sq[buf][tt][d], a.q + (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d);
+      cp_async4(&sk[buf][tt][d], a.k + (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d);
+    }
+    for (int i = tid; i < nt * DR_COLS; i += 128) {
+      const int tt = i / DR_COLS, c = i % DR_COLS;
+      if (blockIdx.x * DR_COLS + c < a.vd)
+        cp_async4(&sv[buf][tt][c], a.v + (size_t)(tb + tt) * v_ld + (size_t)h * a.vd + blockIdx.x * DR_COLS + c);
+    }
+    for (int i = tid; i < nt * 2; i += 128)
+      cp_async4(&sg[buf][i / 2][i % 2], a.gb + ((size_t)(tb + i / 2) * a.heads + h) * 2 + i % 2);
+  };
+  stage(0, t0);
+  cp_commit();
+  int buf = 0;
+  for (int tb = t0; tb < t1; tb += DR_TOK, buf ^= 1) {
+    if (tb + DR_TOK < t1) stage(buf ^ 1, tb + DR_TOK);
+    cp_commit();
+    cp_wait<1>();
+    __syncthreads();
+    const int nt = min(DR_TOK, t1 - tb);
+    for (int tt = 0; tt < nt; ++tt) {
+      float pa = 0.f, pb = 0.f, pc = 0.f;
+      float kr[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        kr[i] = sk[buf][tt][i * DR_LANES + sub];
+        const float qr = sq[buf][tt][i * DR_LANES + sub];
+        pa = fmaf(s[i], kr[i], pa);
+        pb = fmaf(s[i], qr, pb);
+        pc = fmaf(kr[i], qr, pc);
+      }
+#pragma unroll
+      for (int o = DR_LANES / 2; o > 0; o >>= 1) {
+        pa += __shfl_xor_sync(0xffffffffu, pa, o);
+        pb += __shfl_xor_sync(0xffffffffu, pb, o);
+        pc += __shfl_xor_sync(0xffffffffu, pc, o);
+      }
+      const float g = sg[buf][tt][0], beta = sg[buf][tt][1];
+      const float u = __fmul_rn(beta, fmaf(-g, pa, sv[buf][tt][cl]));
+      const float o = fmaf(u, pc, __fmul_rn(g, pb));
+#pragma unroll
+      for (int i = 0; i < R; ++i) s[i] = fmaf(kr[i], u, __fmul_rn(g, s[i]));
+      if (sub == 0 && col_ok) a.out[(size_t)(tb + tt) * v_ld + (size_t)h * a.vd + col] = o;
+    }
+    __syncthreads();   // the stage is free for the copies after the next
+  }
+  cp_wait<0>();
+  if (col_ok) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int row = i * DR_LANES + sub;
+      if (row < a.kd) st[row] = s[i];
+    }
+  }
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_delta_prepare(const void* proj, int ld, const float* taps, int n_taps, const float* kept,
+                                  const int* slots, const int* cu_q, const int* token_request, int heads, int kv_heads,
+                                  int kd, int vd, int beta_col, int a_col, const float* a_log, const float* dt_bias,
+                                  float q_scale, float unit_eps, float* q, float* k, float* v, float* gb, int n_tokens,
+                                  int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && kd > 0 && vd > 0 && n_taps >= 1,
+               "delta_prepare: %d tokens, %d heads over %d query/key heads, sizes %d / %d, %d taps", n_tokens, heads, kv_heads, kd, vd, n_taps);
+  PrepArgs a;
+  a.proj = proj; a.ld = ld; a.taps = taps; a.n_taps = n_taps; a.kept = kept; a.slots = slots; a.cu_q = cu_q;
+  a.token_request = token_request; a.heads = heads; a.kv_heads = kv_heads; a.kd = kd; a.vd = vd; a.beta_col = beta_col;
+  a.a_col = a_col; a.a_log = a_log; a.dt_bias = dt_bias; a.q_scale = q_scale; a.unit_eps = unit_eps; a.q = q; a.k = k;
+  a.v = v; a.gb = gb; a.n_tokens = n_tokens;
+  const long long tasks = (long long)n_tokens * (2 * kv_heads + heads);
+  const long long blocks = (tasks + 3) / 4;
+  TLLM_REQUIRE(blocks <= 2147483647LL, "delta_prepare: %lld rows exceed the grid", tasks);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32) TLLM_LAUNCH("delta_prepare", delta_prepare_kernel<float>, (unsigned)blocks, 128, 0, s, a);
+  else if (dtype == TLLM_BF16) TLLM_LAUNCH("delta_prepare", delta_prepare_kernel<__nv_bfloat16>, (unsigned)blocks, 128, 0, s, a);
+  else TLLM_FAIL(TLLM_ERR_ARG, "delta_prepare: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_conv_state_update(const void* proj, int ld, float* kept, const int* slots, const int* cu_q, int n_taps,
+                                      int channels, int n_requests, int dtype, void* stream) {
+  TLLM_REQUIRE(n_requests > 0 && channels > 0 && n_taps >= 1 && n_requests <= 65535,
+               "conv_state_update: %d requests, %d channels, %d taps", n_requests, channels, n_taps);
+  if (n_taps == 1) return TLLM_OK;
+  const dim3 grid((channels + 127) / 128, n_requests);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    TLLM_LAUNCH("conv_state_update", conv_state_update_kernel<float>, grid, 128, 0, s, (const float*)proj, ld, kept, slots, cu_q, n_taps, channels, n_requests);
+  else if (dtype == TLLM_BF16)
+    TLLM_LAUNCH("conv_state_update", conv_state_update_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)proj, ld, kept, slots, cu_q, n_taps, channels, n_requests);
+  else TLLM_FAIL(TLLM_ERR_ARG, "conv_state_update: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_delta_rule_scan(const float* q, const float* k, const float* v, const float* gb, float* state,
+                                    const int* slots, const int* cu_q, float* out, int heads, int kv_heads, int kd, int vd,
+                                    int n_requests, void* stream) {
+  TLLM_REQUIRE(n_requests > 0 && n_requests <= 65535 && heads > 0 && heads <= 65535 && kv_heads > 0 && heads % kv_heads == 0,
+               "delta_rule_scan: %d requests, %d heads over %d query/key heads", n_requests, heads, kv_heads);
+  TLLM_REQUIRE(kd >= 1 && kd <= 256 && vd >= 1, "delta_rule_scan: key size %d (at most 256), value size %d", kd, vd);
+  ScanArgs a;
+  a.q = q; a.k = k; a.v = v; a.gb = gb; a.state = state; a.slots = slots; a.cu_q = cu_q; a.out = out; a.heads = heads;
+  a.kv_heads = kv_heads; a.kd = kd; a.vd = vd;
+  const dim3 grid((vd + DR_COLS - 1) / DR_COLS, heads, n_requests);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (kd <= 32) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<4>, grid, 128, 0, s, a);
+  else if (kd <= 64) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<8>, grid, 128, 0, s, a);
+  else if (kd <= 128) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<16>, grid, 128, 0, s, a);
+  else TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<32>, grid, 128, 0, s, a);
+  return TLLM_OK;
+}

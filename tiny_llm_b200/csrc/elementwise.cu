@@ -10,17 +10,17 @@ TLLM_DEFINE_LAST_ERROR
 
 namespace tllm {
 
-// ---------------------------------------------------------------- embedding: out[t,:] = table[tokens[t],:]
+// ---------------------------------------------------------------- embedding: out[t,:] = table[tokens[t],:] * scale
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                                 float* __restrict__ out, int n_tokens, int hidden) {
+                                 float* __restrict__ out, int n_tokens, int hidden, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
   const T* row = table + (size_t)tokens[t] * hidden;
   float* dst = out + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = __fmul_rn(to_f32(row[i]), scale);
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -122,12 +122,12 @@ __global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __
   }
 }
 
-// ---------------------------------------------------------------- SiLU(gate) * up
+// ---------------------------------------------------------------- act(gate) * up, act = SiLU (0) or ReLU (1)
 // `gu` rows hold gate and up interleaved in blocks: [2 g B, 2 g B + B) gate, next B up.  With
 // ZERO the source is a float32 accumulation buffer (split-K partial sums land there) that this
 // kernel hands back cleared: every element is read once, by the thread that then zeroes it.
 template <typename TIn, typename TOut, bool ZERO>
-__global__ void silu_mul_kernel(TIn* __restrict__ gu, TOut* __restrict__ out, int m, int inter, int blk) {
+__global__ void silu_mul_kernel(TIn* __restrict__ gu, TOut* __restrict__ out, int m, int inter, int blk, int act) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)m * inter;
@@ -138,7 +138,7 @@ __global__ void silu_mul_kernel(TIn* __restrict__ gu, TOut* __restrict__ out, in
     TIn* src = gu + (size_t)row * 2 * inter + (size_t)g * 2 * blk;
     const float gate = to_f32(src[j]), up = to_f32(src[blk + j]);
     if (ZERO) { src[j] = from_f32<TIn>(0.f); src[blk + j] = from_f32<TIn>(0.f); }
-    out[idx] = from_f32<TOut>((gate / (1.f + expf(-gate))) * up);
+    out[idx] = from_f32<TOut>((act == 1 ? fmaxf(gate, 0.f) : gate / (1.f + expf(-gate))) * up);
   }
 }
 
@@ -523,14 +523,14 @@ extern "C" int tllm_diff_combine(const float* a, const float* lq1, const float* 
 }
 
 extern "C" int tllm_embedding(const int* tokens, const void* table, float* out, int n_tokens, int hidden,
-                              int dtype, void* stream) {
+                              int dtype, float scale, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && hidden > 0, "embedding: empty input (%d tokens, width %d)", n_tokens, hidden);
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)
-    TLLM_LAUNCH("embedding", embedding_kernel<float>, n_tokens, threads, 0, s, tokens, (const float*)table, out, n_tokens, hidden);
+    TLLM_LAUNCH("embedding", embedding_kernel<float>, n_tokens, threads, 0, s, tokens, (const float*)table, out, n_tokens, hidden, scale);
   else if (dtype == TLLM_BF16)
-    TLLM_LAUNCH("embedding", embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden);
+    TLLM_LAUNCH("embedding", embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden, scale);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "embedding: unknown dtype code %d", dtype);
   return TLLM_OK;
@@ -581,7 +581,7 @@ extern "C" int tllm_rms_norm_add(float* x, const float* w, float* resid, int n_r
 // in_dtype: dtype of `gu`; out_dtype: dtype of `out`.  zero_src != 0 (float32 `gu` only): `gu` is a
 // split-K accumulation buffer and is handed back cleared.
 extern "C" int tllm_silu_mul(void* gu, void* out, int m, int inter, int blk, int in_dtype, int out_dtype, int zero_src,
-                             void* stream) {
+                             int act, void* stream) {
   TLLM_REQUIRE(m > 0 && inter > 0 && blk > 0 && inter % blk == 0,
                "silu_mul: %d rows, width %d, block %d (the block must divide the width)", m, inter, blk);
   const size_t total = (size_t)m * inter;
@@ -589,11 +589,11 @@ extern "C" int tllm_silu_mul(void* gu, void* out, int m, int inter, int blk, int
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   cudaStream_t s = (cudaStream_t)stream;
   if (in_dtype == TLLM_F32 && out_dtype == TLLM_F32 && !zero_src)
-    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, float, false>), blocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk);
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, float, false>), blocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk, act);
   else if (in_dtype == TLLM_BF16 && out_dtype == TLLM_BF16 && !zero_src)
-    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16, false>), blocks, threads, 0, s, (__nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk);
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16, false>), blocks, threads, 0, s, (__nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
   else if (in_dtype == TLLM_F32 && out_dtype == TLLM_BF16 && zero_src)
-    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, __nv_bfloat16, true>), blocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk);
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, __nv_bfloat16, true>), blocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "silu_mul: dtype codes %d -> %d with zero_src %d are not built", in_dtype, out_dtype, zero_src);
   return TLLM_OK;

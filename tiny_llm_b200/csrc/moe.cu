@@ -1,7 +1,8 @@
 // Mixture of experts: routing on the device and one grouped product for all experts.
 //
-// moe_route: per token, s_e = sigmoid(z_e); the `top` experts with the largest s_e + correction_e are chosen (ties:
-//   the lower index); their weights are s_e * scale.  One warp per token, 32-bit.
+// moe_route: per token, s_e = sigmoid(z_e), or softmax(z)_e over all experts; the `top` experts with the largest
+//   s_e + correction_e (no correction: s_e) are chosen (ties: the lower index); their weights are s_e * scale.  One
+//   warp per token, 32-bit.
 // moe_align: the (token, choice) pairs of the step, numbered token * top + choice, are grouped by expert into tiles
 //   of `tile` rows: sorted_rows[tile * tile_rows + i] is a pair's number or -1 (padding), tile_expert[tile] the
 //   tile's expert or -1 (no such tile).  The host knows only the upper bound of the tile count.
@@ -24,19 +25,36 @@ __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + er
 constexpr int ROUTE_PER_LANE = 16;   // experts per lane: at most 512 experts
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int n_experts, const float* __restrict__ correction,
-                                 float scale, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens) {
+                                 float scale, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens,
+                                 int softmax) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
   const int lane = threadIdx.x & 31;
   float s[ROUTE_PER_LANE], c[ROUTE_PER_LANE];
+  float zmax = -INFINITY, zsum = 0.f;
+  if (softmax) {   // scores over all experts: exp(z - max) / sum, the sum taken lane by lane and then across the warp
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_experts) zmax = fmaxf(zmax, logits[(size_t)t * ld + e]);
+    }
+    zmax = warp_max(zmax);
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < n_experts ? expf(logits[(size_t)t * ld + e] - zmax) : 0.f;
+      zsum += s[i];
+    }
+    zsum = 1.f / warp_sum(zsum);
+  }
 #pragma unroll
   for (int i = 0; i < ROUTE_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     if (e < n_experts) {
-      s[i] = 1.f / (1.f + expf(-logits[(size_t)t * ld + e]));
-      c[i] = s[i] + correction[e];
+      s[i] = softmax ? s[i] * zsum : 1.f / (1.f + expf(-logits[(size_t)t * ld + e]));
+      c[i] = correction ? s[i] + correction[e] : s[i];
     } else {
       s[i] = 0.f;
       c[i] = -INFINITY;
@@ -339,12 +357,12 @@ __global__ void gelu_kernel(const T* __restrict__ x, T* __restrict__ y, long lon
 using namespace tllm;
 
 extern "C" int tllm_moe_route(const float* logits, int ld, int n_experts, const float* correction, float scale, int top,
-                              int* ids, float* weights, int n_tokens, void* stream) {
+                              int* ids, float* weights, int n_tokens, int softmax, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: %d of %d experts for %d tokens", top, n_experts, n_tokens);
   TLLM_REQUIRE(n_experts <= 32 * ROUTE_PER_LANE, "moe_route: %d experts (at most %d)", n_experts, 32 * ROUTE_PER_LANE);
   const int warps = 4;
   TLLM_LAUNCH("moe_route", moe_route_kernel, (unsigned)((n_tokens + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream,
-              logits, ld, n_experts, correction, scale, top, ids, weights, n_tokens);
+              logits, ld, n_experts, correction, scale, top, ids, weights, n_tokens, softmax);
   return TLLM_OK;
 }
 

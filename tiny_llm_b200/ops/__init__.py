@@ -126,9 +126,10 @@ def trace_dump():
 # ----------------------------------------------------------------------------- elementwise
 
 
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """out[t, :] = table[tokens[t], :] as float32 (the residual stream is 32-bit); accumulate=True adds the rows
-    into `out` instead."""
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+              scale: float = 1.0) -> None:
+    """out[t, :] = table[tokens[t], :] * scale as float32 (the residual stream is 32-bit; the product is taken in
+    32-bit); accumulate=True adds the rows into `out` instead (unscaled)."""
     _need_cuda(tokens, table, out)
     _i32(tokens, "tokens")
     t, h = out.shape
@@ -136,8 +137,13 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, accu
             or tokens.numel() != t:
         raise KernelError("embedding: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _call(lib, lib.tllm_embedding_add if accumulate else lib.tllm_embedding, _ptr(tokens), _ptr(table), _ptr(out), t, h,
-          _code(table.dtype), _stream())
+    if accumulate:
+        if scale != 1.0:
+            raise KernelError("embedding: rows that are added are not scaled")
+        _call(lib, lib.tllm_embedding_add, _ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), _stream())
+        return
+    _call(lib, lib.tllm_embedding, _ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), ctypes.c_float(scale),
+          _stream())
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -251,8 +257,11 @@ def min_gru_scan(zug: torch.Tensor, bias_z: torch.Tensor, bias_u: torch.Tensor, 
           _ptr(summary), _code(zug.dtype), _stream())
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False) -> None:
-    """out[m, g*block + j] = silu(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j].
+GLU_ACTS = {"silu": 0, "relu": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False, act: str = "silu") -> None:
+    """out[m, g*block + j] = act(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j], act = silu or relu.
     consume=True: `gate_up` is a float32 accumulation buffer (split-K sums) and is handed back zeroed."""
     _need_cuda(gate_up, out)
     m, inter = out.shape
@@ -260,8 +269,10 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool
             (consume and gate_up.dtype != torch.float32) or (not consume and gate_up.dtype != out.dtype):
         raise KernelError("silu_mul: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
+    if act not in GLU_ACTS:
+        raise KernelError(f"silu_mul: unknown activation {act!r} (known: {', '.join(GLU_ACTS)})")
     _call(lib, lib.tllm_silu_mul, _ptr(gate_up), _ptr(out), m, inter, block, _code(gate_up.dtype), _code(out.dtype),
-                                  1 if consume else 0, _stream())
+                                  1 if consume else 0, GLU_ACTS[act], _stream())
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
@@ -526,20 +537,21 @@ def gelu(x: torch.Tensor, out: torch.Tensor) -> None:
     _call(lib, lib.tllm_gelu, _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _code(x.dtype), _stream())
 
 
-def moe_route(logits: torch.Tensor, num_experts: int, correction: torch.Tensor, scale: float, ids: torch.Tensor,
-              weights: torch.Tensor) -> None:
-    """Per token: s = sigmoid(logits[t, :num_experts]); ids[t] = the `top` experts with the largest s + correction (ties:
-    the lower index), weights[t] = their s * scale.  logits float32 (further columns are ignored), ids int32 [T, top],
-    weights float32 [T, top]."""
+def moe_route(logits: torch.Tensor, num_experts: int, correction: Optional[torch.Tensor], scale: float, ids: torch.Tensor,
+              weights: torch.Tensor, softmax: bool = False) -> None:
+    """Per token: s = sigmoid(logits[t, :num_experts]), or softmax over the experts with softmax=True; ids[t] = the `top`
+    experts with the largest s + correction (None: s; ties: the lower index), weights[t] = their s * scale.  logits
+    float32 (further columns are ignored), ids int32 [T, top], weights float32 [T, top]."""
     _need_cuda(logits, correction, ids, weights)
     t, top = ids.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[0] != t or logits.shape[1] < num_experts or \
-            correction.dtype != torch.float32 or correction.numel() != num_experts or ids.dtype != torch.int32 or \
+            (correction is not None and (correction.dtype != torch.float32 or correction.numel() != num_experts)) or \
+            ids.dtype != torch.int32 or \
             weights.dtype != torch.float32 or weights.shape != ids.shape or not ids.is_contiguous() or not weights.is_contiguous():
         raise KernelError("moe_route: shapes or dtypes do not fit")
     lib = build.load_library("moe")
     _call(lib, lib.tllm_moe_route, _ptr(logits), logits.stride(0), num_experts, _ptr(correction), ctypes.c_float(scale), top,
-          _ptr(ids), _ptr(weights), t, _stream())
+          _ptr(ids), _ptr(weights), t, 1 if softmax else 0, _stream())
 
 
 def moe_tile_rows(pairs: int, num_experts: int, tensor_cores: bool = False) -> int:
@@ -655,6 +667,145 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.T
     lib = build.load_library("moe")
     _call(lib, lib.tllm_moe_combine, _ptr(y), _ptr(weights), top, _ptr(shared), _ptr(logits),
           0 if logits is None else logits.stride(0), gate_col, _ptr(resid), t, width, _ptr(pair_pos), _stream())
+
+
+# ----------------------------------------------------------------------------- attention without rotate-half, delta rule
+
+
+def qk_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int,
+                     value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                     bias_q: Optional[torch.Tensor] = None, bias_k: Optional[torch.Tensor] = None,
+                     bias_v: Optional[torch.Tensor] = None, norm_q: Optional[torch.Tensor] = None,
+                     norm_k: Optional[torch.Tensor] = None, eps: float = 0.0, stretch_coef: float = 0.0,
+                     stretch_every: int = 0) -> None:
+    """Rows of `proj` begin with num_heads query heads and num_kv_heads key heads of key_dim values, then num_kv_heads
+    value heads of value_dim values.  Biases (float32) are added; with norm weights (float32 [key_dim], shared by the
+    heads) query and key heads become x / sqrt(mean(x^2) + eps) * weight; with stretch_every > 0 the query at position
+    p is multiplied by 1 + stretch_coef * ln(floor((p + 1) / stretch_every) + 1).  Queries are rewritten in place, keys
+    and values go to their pages."""
+    _need_cuda(proj, positions, k_cache, v_cache, slot_mapping, bias_q, bias_k, bias_v, norm_q, norm_k)
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    t = proj.shape[0]
+    if proj.stride(1) != 1 or proj.shape[1] < (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim:
+        raise KernelError("qk_norm_kv_write: the rows of the projection do not fit")
+    _paged("qk_norm_kv_write", k_cache, num_kv_heads, key_dim)
+    _paged("qk_norm_kv_write", v_cache, num_kv_heads, value_dim)
+    if k_cache.dtype != proj.dtype or v_cache.dtype != proj.dtype or k_cache.shape[2] != v_cache.shape[2]:
+        raise KernelError("qk_norm_kv_write: cache dtype or page size does not fit")
+    for name, b, n in (("query bias", bias_q, num_heads * key_dim), ("key bias", bias_k, num_kv_heads * key_dim),
+                       ("value bias", bias_v, num_kv_heads * value_dim), ("query norm", norm_q, key_dim),
+                       ("key norm", norm_k, key_dim)):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != n or not b.is_contiguous()):
+            raise KernelError(f"qk_norm_kv_write: the {name} must be {n} contiguous float32 values")
+    ll = ctypes.c_longlong
+    lib = build.load_library("attention_prep")
+    _call(lib, lib.tllm_qk_norm_kv_write, _ptr(proj), proj.stride(0), num_heads, num_kv_heads, key_dim, value_dim,
+          _ptr(bias_q), _ptr(bias_k), _ptr(bias_v), _ptr(norm_q), _ptr(norm_k), ctypes.c_float(eps),
+          ctypes.c_float(stretch_coef), int(stretch_every), _ptr(positions), _ptr(k_cache), _ptr(v_cache),
+          _ptr(slot_mapping), k_cache.shape[2], ll(k_cache.stride(0)), ll(k_cache.stride(1)), ll(v_cache.stride(0)),
+          ll(v_cache.stride(1)), t, _code(proj.dtype), _stream())
+
+
+def latent_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int, plain_dim: int, rot_part: int,
+                    rank: int, rot_dims: int, freq: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                    q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Rows of `proj`: num_heads query heads of [plain_dim | rot_part] values, then `rank` latent values and rot_part
+    key values shared by the heads.  The latent, normed with `norm_weight`, becomes the first `rank` values of the
+    token's key row and its whole value row; the key's part and every query head's part are rotated pairwise (value
+    2i with 2i + 1, i < rot_dims / 2) by positions[t] * freq[i]; the key part is written behind the latent, the query
+    parts to q_out[t, head, rank:] (q_out [T, num_heads, rank + rot_part])."""
+    _need_cuda(proj, positions, freq, norm_weight, q_out, k_cache, v_cache, slot_mapping)
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    t = proj.shape[0]
+    kd = rank + rot_part
+    if proj.stride(1) != 1 or proj.shape[1] < num_heads * (plain_dim + rot_part) + kd or \
+            q_out.shape != (t, num_heads, kd) or not q_out.is_contiguous() or q_out.dtype != proj.dtype:
+        raise KernelError("latent_kv_write: the rows of the projection or of the query buffer do not fit")
+    _paged("latent_kv_write", k_cache, 1, kd)
+    _paged("latent_kv_write", v_cache, 1, rank)
+    if k_cache.dtype != proj.dtype or v_cache.dtype != proj.dtype or k_cache.shape[2] != v_cache.shape[2] or \
+            norm_weight.dtype != torch.float32 or norm_weight.numel() != rank or \
+            (rot_dims and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rot_dims)):
+        raise KernelError("latent_kv_write: cache, norm weight or frequency table does not fit")
+    ll = ctypes.c_longlong
+    lib = build.load_library("attention_prep")
+    _call(lib, lib.tllm_latent_kv_write, _ptr(proj), proj.stride(0), num_heads, plain_dim, rot_part, rank, rot_dims,
+          _ptr(norm_weight), _ptr(freq if rot_dims else None), ctypes.c_float(eps), _ptr(positions), _ptr(q_out),
+          _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), k_cache.shape[2], ll(k_cache.stride(0)), ll(v_cache.stride(0)),
+          t, _code(proj.dtype), _stream())
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, value_dim: int, out: torch.Tensor) -> None:
+    """out[t, h, :] = x[t, h, :] * sigmoid(gate[t, ...]): `gate` [T, heads * value_dim] gates every value, `gate`
+    [T, heads] every head as a whole.  x float32, gate (a row slice is fine) and out in the engine's dtype."""
+    _need_cuda(x, gate, out)
+    t = x.shape[0]
+    per_head = gate.shape[1] == heads and value_dim != 1
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.shape != (t, heads * value_dim) or out.shape != x.shape or \
+            not out.is_contiguous() or out.dtype != gate.dtype or gate.stride(1) != 1 or gate.shape[0] != t or \
+            gate.shape[1] not in (heads, heads * value_dim):
+        raise KernelError("sigmoid_gate: shapes or dtypes do not fit")
+    lib = build.load_library("attention_prep")
+    _call(lib, lib.tllm_sigmoid_gate, _ptr(x), _ptr(gate), gate.stride(0), 1 if per_head else 0, _ptr(out),
+          ctypes.c_longlong(t), heads, value_dim, _code(out.dtype), _stream())
+
+
+def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, kept: torch.Tensor, batch, heads: int, kv_heads: int,
+                  key_dim: int, value_dim: int, beta_col: int, a_col: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  q_scale: float, unit_eps: float, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch.Tensor) -> None:
+    """The inputs of the delta rule from the fused projection.  The first kv_heads * key_dim * 2 + heads * value_dim
+    columns of `proj` are the channels [queries | keys | values]; each is filtered over time with its row of `taps`
+    (float32 [channels, n]; the last column meets the current token; ahead of the step's tokens stand the inputs in
+    kept[slot] (float32 [slots, n - 1, channels], oldest first)), then SiLU.  Query and key heads are divided by
+    sqrt(sum(x^2) + unit_eps), queries also multiplied by q_scale.  Columns beta_col + h and a_col + h hold the step
+    size's and the decay's inputs: gb[t, h] = (exp(-exp(a_log[h]) softplus(a + dt_bias[h])), sigmoid(b)).  q, k, v, gb
+    are float32."""
+    _need_cuda(proj, taps, kept, a_log, dt_bias, q, k, v, gb)
+    t = proj.shape[0]
+    channels = 2 * kv_heads * key_dim + heads * value_dim
+    n = taps.shape[1]
+    if proj.stride(1) != 1 or proj.shape[1] < max(channels, beta_col + heads, a_col + heads) or \
+            taps.dtype != torch.float32 or taps.shape != (channels, n) or not taps.is_contiguous() or \
+            kept.dtype != torch.float32 or not kept.is_contiguous() or tuple(kept.shape[1:]) != (max(n - 1, 1), channels) or \
+            any(x.dtype != torch.float32 or not x.is_contiguous() for x in (a_log, dt_bias, q, k, v, gb)) or \
+            a_log.numel() != heads or dt_bias.numel() != heads or q.shape != (t, kv_heads * key_dim) or k.shape != q.shape or \
+            v.shape != (t, heads * value_dim) or gb.shape != (t, heads, 2):
+        raise KernelError("delta_prepare: shapes or dtypes do not fit")
+    lib = build.load_library("delta_rule")
+    _call(lib, lib.tllm_delta_prepare, _ptr(proj), proj.stride(0), _ptr(taps), n, _ptr(kept), _ptr(batch.slots),
+          _ptr(batch.cu_q), _ptr(batch.token_request), heads, kv_heads, key_dim, value_dim, beta_col, a_col, _ptr(a_log),
+          _ptr(dt_bias), ctypes.c_float(q_scale), ctypes.c_float(unit_eps), _ptr(q), _ptr(k), _ptr(v), _ptr(gb), t,
+          _code(proj.dtype), _stream())
+
+
+def conv_state_update(proj: torch.Tensor, kept: torch.Tensor, batch, n_taps: int, channels: int) -> None:
+    """kept[slot] <- the last n_taps - 1 inputs of every channel after the step's tokens (what was kept before moves
+    up when the step brought fewer tokens than that)."""
+    _need_cuda(proj, kept)
+    if proj.stride(1) != 1 or proj.shape[1] < channels or kept.dtype != torch.float32 or not kept.is_contiguous() or \
+            tuple(kept.shape[1:]) != (max(n_taps - 1, 1), channels):
+        raise KernelError("conv_state_update: shapes or dtypes do not fit")
+    lib = build.load_library("delta_rule")
+    _call(lib, lib.tllm_conv_state_update, _ptr(proj), proj.stride(0), _ptr(kept), _ptr(batch.slots), _ptr(batch.cu_q),
+          n_taps, channels, batch.num_requests, _code(proj.dtype), _stream())
+
+
+def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch.Tensor, state: torch.Tensor, batch,
+                    heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor) -> None:
+    """Per head and token, in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q, with (g, beta) =
+    gb[t, h]; head h reads query/key head h // (heads / kv_heads).  All float32; state [slots, heads, value_dim,
+    key_dim] (the transpose of S) is carried from step to step."""
+    _need_cuda(q, k, v, gb, state, out)
+    t = q.shape[0]
+    if any(x.dtype != torch.float32 or not x.is_contiguous() for x in (q, k, v, gb, state, out)) or \
+            q.shape != (t, kv_heads * key_dim) or k.shape != q.shape or v.shape != (t, heads * value_dim) or \
+            gb.shape != (t, heads, 2) or out.shape != v.shape or tuple(state.shape[1:]) != (heads, value_dim, key_dim):
+        raise KernelError("delta_rule_scan: shapes or dtypes do not fit")
+    lib = build.load_library("delta_rule")
+    _call(lib, lib.tllm_delta_rule_scan, _ptr(q), _ptr(k), _ptr(v), _ptr(gb), _ptr(state), _ptr(batch.slots),
+          _ptr(batch.cu_q), _ptr(out), heads, kv_heads, key_dim, value_dim, batch.num_requests, _stream())
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -860,11 +1011,23 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
                                         _code(a.dtype), mode, int(linear_skinny), _stream())
 
 
-def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace) -> None:
-    """out = silu(a Wg^T) * (a Wu^T) with Wg, Wu interleaved in `w_gate_up` in row blocks of `block`.
-    With blocks of 128 and more than 128 rows the product and SiLU*up are one tensor-core kernel."""
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace,
+                  act: str = "silu") -> None:
+    """out = act(a Wg^T) * (a Wu^T) with Wg, Wu interleaved in `w_gate_up` in row blocks of `block`; act = silu or relu.
+    With blocks of 128 and more than 128 rows the product and SiLU*up are one tensor-core kernel (SiLU only: another
+    activation takes the product and the element-wise kernel)."""
     m = a.shape[0]
     n2 = w_gate_up.shape[0]
+    if act != "silu":
+        if prefers_split(a, w_gate_up):
+            acc = workspace.get_zeroed("gate_up_f32", (m, n2))
+            linear(a, w_gate_up, acc, accumulate=True)
+            silu_mul(acc, out, block, consume=True, act=act)
+            return
+        gu = workspace.get("gate_up", (m, n2), a.dtype)
+        linear(a, w_gate_up, gu)
+        silu_mul(gu, out, block, act=act)
+        return
     if _tc_ok(a, w_gate_up, out) and block == 128 and m > 128 and n2 % 256 == 0 and out.is_contiguous():
         _need_cuda(a, w_gate_up, out)
         lib = build.load_library("linear_tc")
@@ -1053,18 +1216,22 @@ attention_maps_decode_pairs = int(os.environ.get("TLLM_ATTENTION_MAPS_DECODE_PAI
 def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, maps: int, key_dim: int, value_dim: int,
                          k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, batch,
                          out: torch.Tensor, scale: float, window: Optional[int] = None,
-                         chunk: Optional[int] = None) -> None:
+                         chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> None:
     """Attention with `maps` score maps per head over the same values, key rows of key_dim and value rows of
     value_dim values: query rows [head][map][key_dim] at the front of each `qkv` row, k_cache
     [pages, num_kv_heads * maps, page_size, key_dim], v_cache [pages, num_kv_heads, page_size, value_dim]; out
     [T, num_heads * maps * value_dim] in the cache's dtype or float32.  `chunk`: a key is visible only inside the
-    query's chunk of that many positions (counted from position 0).  `batch`: token_request and positions per token
+    query's chunk of that many positions (counted from position 0).  `sink` (float32 [num_heads]): a learned score
+    per head whose exponential joins the softmax's denominator; it stands for no key and has no value.
+    `batch`: token_request and positions per token
     (the CUDA-core kernel); cu_q, q_start per request, num_requests, max_q_len (the tensor-core kernel).
     bfloat16 with a float32 output and sizes that are multiples of 16 runs on the tensor cores, everything else on
     the CUDA cores in 32-bit."""
-    _need_cuda(qkv, k_cache, v_cache, block_table, out)
+    _need_cuda(qkv, k_cache, v_cache, block_table, out, sink)
     _i32(block_table, "block_table")
     t = qkv.shape[0]
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_contiguous()):
+        raise KernelError("paged_attention_maps: the sink is one float32 per head")
     if out.shape != (t, num_heads * maps * value_dim) or not out.is_contiguous() or \
             out.dtype not in (qkv.dtype, torch.float32) or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or \
             k_cache.stride(3) != 1 or k_cache.stride(2) != key_dim or k_cache.shape[1] != num_kv_heads * maps or \
@@ -1082,7 +1249,8 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
               _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
               num_kv_heads, maps, key_dim, value_dim, k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)),
               ctypes.c_longlong(k_cache.stride(1)), ctypes.c_longlong(v_cache.stride(0)),
-              ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale), int(window or 0), int(chunk or 0), _stream())
+              ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale), int(window or 0), int(chunk or 0), _ptr(sink),
+              _stream())
         return
     lib = build.load_library("attention_generic")
     _call(lib, lib.tllm_paged_attention_maps,
@@ -1091,7 +1259,7 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
           value_dim, k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
           ctypes.c_longlong(v_cache.stride(0)), ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale),
           int(window or 0), int(chunk or 0), _code(qkv.dtype), 1 if out.dtype == torch.float32 else 0,
-          -1 if generic_attention_split is None else int(generic_attention_split), _stream())
+          -1 if generic_attention_split is None else int(generic_attention_split), _ptr(sink), _stream())
 
 
 def attention_tc_timing(head_dim: int = 64) -> Optional[dict]:
@@ -1148,8 +1316,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
                                 _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream())
 
 
-ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "recurrence", "linear_attention",
-                 "window_attention", "moe", "sampling")
+ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "attention_prep", "recurrence",
+                 "linear_attention", "delta_rule", "window_attention", "moe", "sampling")
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use

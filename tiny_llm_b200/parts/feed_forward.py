@@ -41,9 +41,14 @@ class SwiGLU:
     graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
     def __init__(self, hidden_size: int, intermediate_size: int,
-                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight"), out_scale: float = 1.0):
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight"), out_scale: float = 1.0,
+                 act: str = "silu"):
         """`names`: what the gate, up and down matrices are called behind the part's prefix.  `out_scale`: a
-        constant the part's output is multiplied by; it is folded into the down matrix when that is loaded."""
+        constant the part's output is multiplied by; it is folded into the down matrix when that is loaded.
+        `act`: the gate's activation, "silu" or "relu" (m = (act(y Wg^T) * (y Wu^T)) Wd^T)."""
+        if act not in ops.GLU_ACTS:
+            raise ValueError(f"unknown gate activation {act!r}; known: {', '.join(ops.GLU_ACTS)}")
+        self.act = act
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.names = tuple(names)
@@ -66,7 +71,7 @@ class SwiGLU:
     def forward(self, ctx, h, resid) -> None:
         t = h.shape[0]
         act = ctx.workspace.get("ffn_act", (t, self.intermediate_size), ctx.dtype)
-        ops.linear_swiglu(h, self.w_gate_up, act, self.block, ctx.workspace)
+        ops.linear_swiglu(h, self.w_gate_up, act, self.block, ctx.workspace, act=self.act)
         ops.linear(act, self.w_down, resid, accumulate=True)
 
 

@@ -66,6 +66,66 @@ class Block:
 register_block("pre_norm", Block)
 
 
+class SandwichBlock:
+    """Norms on both sides of each branch: x += norm1_out(mixer(norm1(x))); x += norm2_out(ffn(norm2(x))).  The two
+    norms behind the branches are named in `LayerSpec.more` under the roles "norm1_out" and "norm2_out" (the second
+    only when the layer has a feed-forward).  A branch adds its output into a zeroed float32 buffer, whose norm is
+    then added into the stream by one kernel that also hands the buffer back zeroed."""
+
+    def __init__(self, spec: LayerSpec, shares_cache: bool = False):
+        more = {role: (family, part, name) for role, family, part, name in spec.more}
+        for role in ("norm1", "mixer"):
+            if getattr(spec, role) is None:
+                raise ValueError(f"layer {spec.prefix!r}: a sandwich block needs a {role}")
+        if "norm1_out" not in more or (spec.ffn is not None) != ("norm2_out" in more) or \
+                (spec.ffn is None) != (spec.norm2 is None):
+            raise ValueError(f"layer {spec.prefix!r}: a sandwich block has a norm behind each of its branches "
+                             f"(roles norm1_out, norm2_out) and one ahead of it")
+        if spec.residual_scale != 1.0:
+            raise ValueError(f"layer {spec.prefix!r}: a normed branch has no use for a residual scale")
+        self.spec = spec
+        self.norm1 = build_part("norm", spec.norm1)
+        self.mixer = build_part("mixer", spec.mixer, **({"shares_cache": True} if shares_cache else {}))
+        self.norm1_out = build_part("norm", more["norm1_out"][1])
+        self.norm2 = self.ffn = self.norm2_out = None
+        if spec.ffn is not None:
+            self.norm2 = build_part("norm", spec.norm2)
+            self.ffn = build_part("ffn", spec.ffn)
+            self.norm2_out = build_part("norm", more["norm2_out"][1])
+        self._out_names = {role: more[role][2] for role in ("norm1_out", "norm2_out") if role in more}
+        self.hidden_size = None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm1_out, self.norm2, self.ffn, self.norm2_out) if p is not None]
+
+    def _named(self):
+        p, s = self.spec.prefix, self.spec
+        named = [(self.norm1, p + s.norm1_name), (self.mixer, p + s.mixer_prefix), (self.norm1_out, p + self._out_names["norm1_out"])]
+        if self.ffn is not None:
+            named += [(self.norm2, p + s.norm2_name), (self.ffn, p + s.ffn_prefix), (self.norm2_out, p + self._out_names["norm2_out"])]
+        return named
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [w for part, name in self._named() for w in part.weight_specs(name)]
+
+    def load(self, weights) -> None:
+        for part, name in self._named():
+            part.load(name, weights)
+
+    def forward(self, ctx, resid, cache) -> None:
+        h = self.norm1.forward(ctx, resid)
+        branch = ctx.workspace.get_zeroed("branch_out", tuple(resid.shape))
+        self.mixer.forward(ctx, h, branch, cache)
+        self.norm1_out.add_into(ctx, branch, resid)
+        if self.ffn is not None:
+            h = self.norm2.forward(ctx, resid)
+            self.ffn.forward(ctx, h, branch)
+            self.norm2_out.add_into(ctx, branch, resid)
+
+
+register_block("sandwich_norm", SandwichBlock)
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
@@ -75,6 +135,8 @@ class DecoderModel:
             if call.reads_cache_of is not None and not 0 <= call.reads_cache_of < pos:
                 raise ValueError(f"run order entry {pos} reads the cache of entry {call.reads_cache_of}, "
                                  f"which does not run before it")
+        if spec.embedding_scale != 1.0 and any(c.add_embedding for c in spec.order):
+            raise ValueError("a run order that adds the embedding output again takes the table's rows as they are")
         if spec.after_embedding is not None and any(c.add_embedding for c in spec.order):
             raise ValueError("a run order that adds the embedding output again cannot be combined with a hook that "
                              "rewrites the stream after the embedding")
@@ -144,7 +206,7 @@ class DecoderModel:
         s = self.spec
         b = ctx.batch
         resid = ctx.workspace.get("resid", (b.num_tokens, s.hidden_size), torch.float32)
-        ops.embedding(b.tokens, self.embed, resid)
+        ops.embedding(b.tokens, self.embed, resid, scale=s.embedding_scale)
         if self.after_embedding is not None:
             self.after_embedding.forward(ctx, resid)
         for pos, call in enumerate(s.order):

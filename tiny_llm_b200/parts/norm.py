@@ -1,5 +1,6 @@
 """Norms.  RMSNorm: y_j = (w_j x_j) / sqrt(mean_j(x_j^2) + eps), statistics in 32-bit
-(tiny_llm/ops/cuda/norm.cu:16-49).  Any width; the reference stops at 2048."""
+(tiny_llm/ops/cuda/norm.cu:16-49).  Any width; the reference stops at 2048.  With `one_plus` the stored weight lies
+around zero and the norm multiplies by 1 + w_j."""
 from __future__ import annotations
 
 from .. import ops
@@ -10,18 +11,27 @@ from .registry import register_part
 class RMSNorm:
     graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
-    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight"):
-        """`weight_suffix`: what the weight is called behind the part's name ("" when the name is the tensor's)."""
+    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight", one_plus: bool = False):
+        """`weight_suffix`: what the weight is called behind the part's name ("" when the name is the tensor's).
+        `one_plus`: the norm multiplies by 1 + the stored weight (added once, in 32-bit, when the weight is loaded)."""
         self.size = size
         self.eps = float(eps)
         self.weight_suffix = weight_suffix
+        self.one_plus = one_plus
         self.weight = None
 
     def weight_specs(self, prefix: str):
-        return [WeightSpec(prefix + self.weight_suffix, (self.size,), FLOAT32)]
+        init = {"init": ("normal", 0.1)} if self.one_plus else {}
+        return [WeightSpec(prefix + self.weight_suffix, (self.size,), FLOAT32, **init)]
 
     def load(self, prefix: str, weights) -> None:
-        self.weight = weights[prefix + self.weight_suffix]
+        w = weights[prefix + self.weight_suffix]
+        self.weight = (w + 1.0).contiguous() if self.one_plus else w
+
+    def add_into(self, ctx, branch, resid) -> None:
+        """resid += norm(branch): for a block that norms a branch's output before it joins the stream.  `branch` is a
+        zeroed float32 buffer that products added into; it is handed back zeroed."""
+        ops.rms_norm_add(branch, self.weight, self.eps, 1.0, resid)
 
     def forward(self, ctx, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]

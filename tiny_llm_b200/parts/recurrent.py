@@ -194,5 +194,83 @@ class GatedLinearAttention(LinearAttention):
         return {"gate": z, "gate_bias": self.b_a2, "inv_tau": 1.0 / self.tau}
 
 
+class GatedDeltaRule:
+    """The gated delta rule: per head a matrix state that is decayed, corrected towards the current value along the
+    current key, and read out with the query,
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (the read-out sees the token's write)
+    with beta = sigmoid(Wb h), g = exp(-exp(A_log) softplus(Wa h + dt_bias)), one of each per head and token.  q and k
+    have `num_kv_heads` heads (head h reads head h // (heads / kv_heads)), v has `num_heads`; each of q, k, v passes a
+    short causal convolution over time (a filter of `taps` values per channel, stored `<tensor>.conv`, its last column
+    at the current token, no bias) and SiLU; q and k are made unit vectors per head, x / sqrt(sum(x^2) + unit_eps), q
+    also times key_dim^(-1/2).  Every head's o is divided by its root mean square, multiplied by a weight of the value
+    size and by silu(Wg h), and projected.
+
+    All input matrices are one product ([q | k | v | g | b | a] rows).  Per request the mixer keeps two things in the
+    state slot, both 32-bit: S transposed ([heads, value, key]) and the last taps - 1 inputs of every convolution
+    channel.  Decays, step sizes, unit norms, the recurrence and the per-head norm are 32-bit."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, taps: int,
+                 eps: float, unit_eps: float = 1e-6, out_scale: float = 1.0, shares_cache: bool = False):
+        if shares_cache:
+            raise ValueError("a recurrent mixer's state cannot be read by another layer call")
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} query/key heads evenly")
+        if taps < 1:
+            raise ValueError("a convolution has at least one tap")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.key_dim, self.value_dim, self.taps = key_dim, value_dim, taps
+        self.eps, self.unit_eps = float(eps), float(unit_eps)
+        self.out_scale = float(out_scale)
+        self.qk = num_kv_heads * key_dim
+        self.vg = num_heads * value_dim
+        self.channels = 2 * self.qk + self.vg
+        self.w_in = self.w_o = self.w_taps = self.w_norm = self.a_log = self.dt_bias = None
+
+    def cache_need(self):
+        return (StateNeed((self.num_heads, self.value_dim, self.key_dim), torch.float32),
+                StateNeed((max(self.taps - 1, 1), self.channels), torch.float32))
+
+    def weight_specs(self, prefix: str):
+        h, nh = self.hidden_size, self.num_heads
+        taps = ("normal", 0.5)
+        return [WeightSpec(prefix + "q", (self.qk, h), COMPUTE), WeightSpec(prefix + "q.conv", (self.qk, self.taps), FLOAT32, init=taps),
+                WeightSpec(prefix + "k", (self.qk, h), COMPUTE), WeightSpec(prefix + "k.conv", (self.qk, self.taps), FLOAT32, init=taps),
+                WeightSpec(prefix + "v", (self.vg, h), COMPUTE), WeightSpec(prefix + "v.conv", (self.vg, self.taps), FLOAT32, init=taps),
+                WeightSpec(prefix + "b", (nh, h), COMPUTE), WeightSpec(prefix + "a", (nh, h), COMPUTE),
+                WeightSpec(prefix + "A_log", (nh,), FLOAT32, init=("uniform", -3.0, 0.5)),
+                WeightSpec(prefix + "dt_bias", (nh,), FLOAT32, init=("normal", 1.0)),
+                WeightSpec(prefix + "norm", (self.value_dim,), FLOAT32, init=("uniform", 0.5, 1.5)),
+                WeightSpec(prefix + "g", (self.vg, h), COMPUTE), WeightSpec(prefix + "o", (h, self.vg), COMPUTE)]
+
+    def load(self, prefix: str, weights) -> None:
+        self.w_in = torch.cat([weights[prefix + n] for n in ("q", "k", "v", "g", "b", "a")], dim=0).contiguous()
+        self.w_taps = torch.cat([weights[prefix + n + ".conv"] for n in ("q", "k", "v")], dim=0).contiguous()
+        self.w_o = scaled_matrix(weights[prefix + "o"], self.out_scale)
+        self.w_norm, self.a_log, self.dt_bias = weights[prefix + "norm"], weights[prefix + "A_log"], weights[prefix + "dt_bias"]
+
+    def forward(self, ctx, h, resid, cache) -> None:
+        t = h.shape[0]
+        nh, nkv, kd, vd, ws = self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim, ctx.workspace
+        state, kept = cache
+        c, vg = self.channels, self.vg
+        width = c + vg + 2 * nh
+        proj = ws.get("lin_attn_in", (t, -(-width // 8) * 8), ctx.dtype)[:, :width]
+        ops.linear(h, self.w_in, proj, cluster_slices=True)
+        q = ws.get("delta_q", (t, self.qk), torch.float32)
+        k = ws.get("delta_k", (t, self.qk), torch.float32)
+        v = ws.get("delta_v", (t, vg), torch.float32)
+        gb = ws.get("delta_gb", (t, nh, 2), torch.float32)
+        ops.delta_prepare(proj, self.w_taps, kept.state, ctx.batch, nh, nkv, kd, vd, c + vg, c + vg + nh, self.a_log,
+                          self.dt_bias, kd ** -0.5, self.unit_eps, q, k, v, gb)
+        ops.conv_state_update(proj, kept.state, ctx.batch, self.taps, c)
+        o = ws.get("lin_attn_o", (t, vg), torch.float32)
+        ops.delta_rule_scan(q, k, v, gb, state.state, ctx.batch, nh, nkv, kd, vd, o)
+        y = ws.get("lin_attn_y", (t, vg), ctx.dtype)
+        ops.head_norm_gate(o, self.w_norm, proj[:, c:c + vg], nh, vd, self.eps, y)
+        ops.linear(y, self.w_o, resid, accumulate=True)
+
+
+register_part("mixer", "gated_delta_rule", GatedDeltaRule)
 register_part("mixer", "retention", Retention)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
