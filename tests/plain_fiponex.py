@@ -93,13 +93,17 @@ def query_stretch(pos, coef, every):
     return 1.0 + coef * torch.log(torch.floor((pos.to(torch.float64) + 1.0) / every) + 1.0)
 
 
-def rotate_pairs(x, pos, dims, base):
-    """x [T, rows, D]: values (2i, 2i + 1), i < dims / 2, of every row turn by pos * base^(-2i / dims)."""
+def rotate_pairs(x, pos, dims, base, angles32=False):
+    """x [T, rows, D]: values (2i, 2i + 1), i < dims / 2, of every row turn by pos * base^(-2i / dims).  `angles32`:
+    the angle is the 32-bit product of the position and the 32-bit frequency, as the design computes it (at position
+    30,000 that differs from the exact angle by a thousandth of a radian)."""
     if not dims:
         return x
     i = torch.arange(dims // 2, dtype=torch.float64)
     f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
     a = pos.to(torch.float64)[:, None, None] * f[None, None, :]
+    if angles32:
+        a = (pos.to(torch.float32)[:, None, None] * f.to(torch.float32)[None, None, :]).to(torch.float64)
     c, s = torch.cos(a).to(x.dtype), torch.sin(a).to(x.dtype)
     u, v = x[..., 0:dims:2], x[..., 1:dims:2]
     out = x.clone()
