@@ -16,7 +16,8 @@ roofline of every decode point, and the clocks seen while timing.
 Dunelix model at the TinyLlama layer sizes beside the Llama decoder at equal sizes, and its kernels alone beside their
 like kernels, each against its roofline (`--only decode` with it: the decode points alone).  `--design zozenex` does
 the same for a Zozenex model (retention and gated linear attention, window attention with pooled blocks, routed
-experts) beside the Dunelix model at equal width, layers and vocabulary."""
+experts) beside the Dunelix model at equal width, layers and vocabulary, `--design fiponex` for a Fiponex model (gated
+delta rule, latent attention, attention with a sink, dense and routed gated feed-forwards) beside the Zozenex model."""
 import argparse
 import json
 import os
@@ -716,6 +717,231 @@ def zozenex_kernels(dtype, device, pk, tokens=2048):
     return out
 
 
+# `--design fiponex`: a Fiponex model (gated delta rule layers, latent attention with a window, grouped-query attention with
+# a sink, sandwich norms, dense gated feed-forwards and softmax-routed gated experts) at the same width, layers and
+# vocabulary, beside the Zozenex model above (the closest design the engine has: matrix-state recurrences, a window
+# attention every fourth layer, routed experts).
+def fiponex_shape(layers=DESIGN_LAYERS, width=2048, vocab=32000, ff=5632, window=1024):
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 32, "top": 4}}
+    dense = {"kind": "dense", "ff": ff}
+    delta = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}
+    latent = {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 128 ** -0.5,
+              "mask": {"size": window}, "rot": {"dims": 64, "base": 10000.0}}
+    att = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    kinds = [("delta", delta, dense), ("delta", delta, moe), ("latent_attention", latent, moe), ("attention", att, dense)]
+    return {"architecture": "Fiponex", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-6},
+            "initializer_range": 0.02,
+            "layers": [{"type": k, "mixer": m, "mlp": f} for k, m, f in (kinds[i % 4] for i in range(layers))]}
+
+
+def fiponex_decode_bytes(model, runner, batch, mean_ctx, itemsize):
+    """What a decode step must move: the weights once (of the experts only those that the batch's tokens are expected
+    to choose: E (1 - (1 - top / E)^batch) of E), the cached rows a request can see (its window where the layer has
+    one), and the recurrent states read and written."""
+    total = spec_weight_bytes(model, itemsize)
+    for blk in model.blocks:
+        f = blk.ffn
+        if f is None or not hasattr(f, "num_experts"):
+            continue
+        expert = (3 if f.glu is not None else 2) * f.expert_size * f.hidden_size * itemsize
+        chosen = f.num_experts * (1.0 - (1.0 - f.top / f.num_experts) ** batch)
+        total += (chosen - f.num_experts) * expert     # spec_weight_bytes counts every expert
+    for g in runner.cache.groups:
+        seen = mean_ctx if g.need.window is None else min(mean_ctx, g.need.window)
+        total += batch * seen * g.bytes_per_token(itemsize)
+    for n in runner.cache.slots.needs:
+        numel = 1
+        for d in n.shape:
+            numel *= d
+        total += 2 * batch * 4 * numel
+    return int(total)
+
+def fiponex_kernels(dtype, device, pk, tokens=2048):
+    """The design's kernels alone at the sizes of one layer of the --design shape and `tokens` tokens of one prompt, and
+    their like kernels of the Zozenex and Dunelix paths: microseconds, achieved GB/s or TFLOP/s, share of the peak."""
+    import types
+    import torch
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import Workspace
+    t, width, page, window = tokens, 2048, PAGE, 1024
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    rnd = lambda *shape: torch.randn(*shape, device=device).to(dtype)
+    out = {}
+    isz = 2 if dtype == torch.bfloat16 else 4
+
+    def mem(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+
+    def flop(name, us, flops):
+        out[name] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+
+    ws = Workspace(torch.device(device))
+    pages = -(-t // page)
+    table = i32([list(range(pages))])
+    slots, pos = i32(list(range(t))), i32(list(range(t)))
+    meta = types.SimpleNamespace(token_request=i32([0] * t), positions=pos, cu_q=i32([0, t]), q_start=i32([0]), slots=i32([1]),
+                                 num_requests=1, num_tokens=t, max_q_len=t, max_kv_len=t, num_leading_decodes=0)
+
+    # the gated delta rule: filters + unit norms + decays, the kept inputs, the recurrence, the per-head norm
+    h, kvh, kd, vd, taps = 16, 8, 128, 128, 4
+    ch = 2 * kvh * kd + h * vd
+    proj = rnd(t, ch + h * vd + 2 * h)
+    w_taps = torch.randn(ch, taps, device=device) * 0.5
+    kept = torch.zeros(4, taps - 1, ch, device=device)
+    q, k = torch.empty(t, kvh * kd, device=device), torch.empty(t, kvh * kd, device=device)
+    v, gb = torch.empty(t, h * vd, device=device), torch.empty(t, h, 2, device=device)
+    a_log, dt_bias = torch.zeros(h, device=device), torch.zeros(h, device=device)
+    mem("delta_prepare (4 taps, unit norms, decays)", time_kernel(lambda: ops.delta_prepare(
+        proj, w_taps, kept, meta, h, kvh, kd, vd, ch + h * vd, ch + h * vd + h, a_log, dt_bias, kd ** -0.5, 1e-6, q, k, v, gb), flush),
+        t * ch * (isz + 4))
+    mem("conv_state_update", time_kernel(lambda: ops.conv_state_update(proj, kept, meta, taps, ch), flush), (taps - 1) * ch * (isz + 4))
+    state = torch.zeros(4, h, vd, kd, device=device)
+    o = torch.empty(t, h * vd, device=device)
+    scan_bytes = t * (2 * kvh * kd + 2 * h * vd + 2 * h) * 4
+    scan_us = time_kernel(lambda: ops.delta_rule_scan(q, k, v, gb, state, meta, h, kvh, kd, vd, o), flush)
+    mem("delta_rule_scan (16 heads, keys 128, values 128)", scan_us, scan_bytes)
+    out["delta_rule_scan (16 heads, keys 128, values 128)"]["fp32_tflops"] = round(t * h * kd * vd * 8.0 / scan_us / 1e6, 2)
+    state.zero_()
+    lq, lk, lv = rnd(t, h * kd), rnd(t, h * kd), rnd(t, h * vd)
+    lstate = torch.zeros(4, h, kd, vd, device=device)
+    lkw = {"head_decay": torch.full((h,), 0.97, device=device)}
+    like_us = time_kernel(lambda: ops.linear_attention_scan(lq, lk, lv, h, kd, vd, lstate, meta, o, 1.0, 0.125, workspace=ws, **lkw), flush)
+    mem("linear_attention_scan (like; 16 heads, keys 128, values 128)", like_us, t * h * ((2 * kd + vd) * isz + vd * 4))
+    out["linear_attention_scan (like; 16 heads, keys 128, values 128)"]["fp32_tflops"] = round(t * h * kd * vd * 4.0 / like_us / 1e6, 2)
+    g = rnd(t, h * vd)
+    y = torch.empty(t, h * vd, dtype=dtype, device=device)
+    wn = torch.ones(vd, device=device)
+    mem("head_norm_gate (shared with the like)", time_kernel(lambda: ops.head_norm_gate(o, wn, g, h, vd, 1e-6, y), flush), t * h * vd * (4 + 2 * isz))
+
+    # grouped-query attention with a sink: biases + head norms + stretch + cache write, attention, the gate
+    h, kvh, kd, vd = 16, 4, 128, 128
+    width_in = (h + kvh) * kd + kvh * vd + h * vd
+    qkv = rnd(t, width_in)
+    kc = torch.zeros(pages, kvh, page, kd, dtype=dtype, device=device)
+    vc = torch.zeros(pages, kvh, page, vd, dtype=dtype, device=device)
+    bq, bk, bv = torch.zeros(h * kd, device=device), torch.zeros(kvh * kd, device=device), torch.zeros(kvh * vd, device=device)
+    nq, nk = torch.ones(kd, device=device), torch.ones(kd, device=device)
+    mem("qk_norm_kv_write (biases, head norms, stretch)", time_kernel(lambda: ops.qk_norm_kv_write(
+        qkv, pos, h, kvh, kd, vd, kc, vc, slots, bq, bk, bv, nq, nk, eps=1e-6, stretch_coef=0.1, stretch_every=1024), flush),
+        t * isz * (h * kd * 2 + (kvh * kd + kvh * vd) * 2))
+    att = torch.empty(t, h * vd, dtype=torch.float32, device=device)
+    sink = torch.zeros(h, device=device)
+    pairs = t * (t + 1) // 2
+    flop("attention with a sink (16 heads of 128, causal)", time_kernel(lambda: ops.paged_attention_maps(
+        qkv, h, kvh, 1, kd, vd, kc, vc, table, meta, att, kd ** -0.5, None, None, sink=sink), flush, repeats=5), 2.0 * pairs * h * (kd + vd))
+    gated = torch.empty(t, h * vd, dtype=dtype, device=device)
+    off = (h + kvh) * kd + kvh * vd
+    mem("sigmoid_gate (per value)", time_kernel(lambda: ops.sigmoid_gate(att, qkv[:, off:off + h * vd], h, vd, gated), flush), t * h * vd * (4 + 2 * isz))
+    gu = rnd(t, 2 * h * vd)
+    mem("silu_mul (like)", time_kernel(lambda: ops.silu_mul(gu, gated, 128), flush), t * h * vd * 3 * isz)
+
+    # latent attention: norm + rotation + cache write, the queries into the latent's space, attention over one shared
+    # row per token (key row 256 = latent 192 + rotated 64, value row 192), the values' projection per head
+    h, nd, rd, lvd, rank = 16, 64, 64, 128, 192
+    lkd = rank + rd
+    lproj = rnd(t, -(-(h * (nd + rd) + lkd + h) // 8) * 8)
+    lkc = torch.zeros(pages, 1, page, lkd, dtype=dtype, device=device)
+    lvc = torch.zeros(pages, 1, page, rank, dtype=dtype, device=device)
+    q_lat = torch.zeros(t, h, lkd, dtype=dtype, device=device)
+    freq = torch.pow(torch.tensor(10000.0), -torch.arange(rd // 2, dtype=torch.float32) * 2 / rd).to(device)
+    wl = torch.ones(rank, device=device)
+    mem("latent_kv_write (norm, pair rotation)", time_kernel(lambda: ops.latent_kv_write(
+        lproj, pos, h, nd, rd, rank, rd, freq, wl, 1e-6, q_lat, lkc, lvc, slots), flush), t * isz * (h * rd * 2 + lkd * 2 + rank))
+    w_uk_t = [rnd(rank, nd) for _ in range(h)]
+    w_uv = [rnd(lvd, rank) for _ in range(h)]
+
+    def absorb():
+        for i in range(h):
+            ops.linear(lproj[:, i * (nd + rd):i * (nd + rd) + nd], w_uk_t[i], q_lat[:, i, :rank])
+    flop("latent query products (16 heads, 64 -> 192)", time_kernel(absorb, flush), 2.0 * t * h * nd * rank)
+    latt = torch.empty(t, h * rank, dtype=torch.float32, device=device)
+    wpairs = sum(min(p + 1, window) for p in range(t))
+    flop("latent attention (16 heads, key row 256, value row 192, window 1024)", time_kernel(lambda: ops.paged_attention_maps(
+        q_lat.view(t, h * lkd), h, 1, 1, lkd, rank, lkc, lvc, table, meta, latt, 0.0884, window, None, sink=sink), flush, repeats=5),
+        2.0 * wpairs * h * (lkd + rank))
+    lg = torch.empty(t, h * rank, dtype=dtype, device=device)
+    mem("sigmoid_gate (per head)", time_kernel(lambda: ops.sigmoid_gate(latt, lproj[:, h * (nd + rd) + lkd:h * (nd + rd) + lkd + h], h, rank, lg), flush),
+        t * h * rank * (4 + isz))
+    lout = torch.empty(t, h * lvd, dtype=dtype, device=device)
+
+    def values_up():
+        for i in range(h):
+            ops.linear(lg[:, i * rank:(i + 1) * rank], w_uv[i], lout[:, i * lvd:(i + 1) * lvd])
+    flop("latent value products (16 heads, 192 -> 128)", time_kernel(values_up, flush), 2.0 * t * h * rank * lvd)
+    # like: the Zozenex window attention with its rotation kernel, the Dunelix attention with two maps
+    zh, zkv, zkd, zvd, pool = 16, 4, 64, 128, 64
+    zq = rnd(t, (zh + zkv) * zkd + zkv * zvd)
+    zk = torch.zeros(pages, zkv, page, zkd, dtype=dtype, device=device)
+    zv = torch.zeros(pages, zkv, page, zvd, dtype=dtype, device=device)
+    pkc, pvc = torch.zeros_like(zk), torch.zeros_like(zv)
+    fk = torch.pow(torch.tensor(10000.0), -torch.arange(zkd // 2, dtype=torch.float32) * 2 / zkd).to(device)
+    fv = torch.pow(torch.tensor(10000.0), -torch.arange(zvd // 2, dtype=torch.float32) * 2 / zvd).to(device)
+    mem("rope_halves_kv_write (like)", time_kernel(lambda: ops.rope_halves_kv_write(zq, pos, fk, zkd, fv, zh, zkv, zkv, zkd, zvd, zk, zv, slots), flush),
+        t * isz * (zh * zkd * 2 + (zkv * zkd + zkv * zvd) * 2))
+    zo = torch.empty(t, zh * zvd, dtype=dtype, device=device)
+    hb = torch.zeros(zh, device=device)
+    zpairs = sum(min(p + 1, window) + max(0, (p - window - pool + 1) // pool + 1 if p - window - pool + 1 >= 0 else 0) for p in range(t))
+    flop("window_pool_attention (like; window 1024, pool 64)", time_kernel(lambda: ops.window_pool_attention(
+        zq, zh, zkv, zkd, zvd, zk, zv, table, pkc, pvc, table, meta, zo, 0.125, 30.0, hb, window, pool, fv), flush, repeats=5),
+        2.0 * zpairs * zh * (zkd + zvd))
+    maps = 2
+    dq = rnd(t, (zh + zkv) * maps * zkd + zkv * zvd)
+    dk = torch.zeros(pages, zkv * maps, page, zkd, dtype=dtype, device=device)
+    per_map = torch.empty(t, zh * maps * zvd, dtype=torch.float32, device=device)
+    dpairs = sum(min(p % 1024, p) + 1 for p in range(t))
+    flop("attention, two maps, chunk 1024 (like)", time_kernel(lambda: ops.paged_attention_maps(
+        dq, zh, zkv, maps, zkd, zvd, dk, zv, table, meta, per_map, 0.125, None, 1024), flush), 2.0 * dpairs * zh * maps * (zkd + zvd))
+
+    # norms and the dense gate
+    x = torch.randn(t, width, device=device)
+    resid = torch.zeros(t, width, device=device)
+    w1 = torch.ones(width, device=device)
+    yy = torch.empty(t, width, dtype=dtype, device=device)
+    mem("rms_norm_add (the norm behind a branch; shared with the like)", time_kernel(lambda: ops.rms_norm_add(x, w1, 1e-6, 1.0, resid), flush), t * width * 16)
+    mem("rms_norm (shared with the like)", time_kernel(lambda: ops.rms_norm(x, w1, 1e-6, yy), flush), t * width * (4 + isz))
+    ff = 5632
+    du = rnd(t, 2 * ff)
+    da = torch.empty(t, ff, dtype=dtype, device=device)
+    mem("silu_mul with relu (dense gate; shared)", time_kernel(lambda: ops.silu_mul(du, da, 128, act="relu"), flush), t * ff * 3 * isz)
+
+    # the experts: softmax routing and grouping, the gated grouped products on tcgen05, the combine
+    experts, top, ff = 32, 4, 1408
+    h_in = rnd(t, width)
+    logits = torch.randn(t, experts, device=device)
+    ids = torch.empty(t, top, dtype=torch.int32, device=device)
+    wts = torch.empty(t, top, device=device)
+    t128 = ops.moe_max_tiles(t * top, experts, ops.MOE_TC_TILE)
+    rows128 = torch.empty(t128 * 128, dtype=torch.int32, device=device)
+    texp128 = torch.empty(t128, dtype=torch.int32, device=device)
+    pos128 = torch.empty(t * top, dtype=torch.int32, device=device)
+
+    def route(softmax):
+        ops.moe_route(logits, experts, None, 1.0, ids, wts, softmax=softmax)
+        ops.moe_align(ids, experts, 128, rows128, texp128, pos128)
+    mem("moe_route (sigmoid; like) + moe_align", time_kernel(lambda: route(False), flush), t * (experts * 4 + top * 16))
+    mem("moe_route (softmax) + moe_align", time_kernel(lambda: route(True), flush), t * (experts * 4 + top * 16))
+    if dtype == torch.bfloat16:
+        w_up = (torch.randn(experts, 2 * ff, width, device=device) * 0.02).to(dtype)
+        w_down = (torch.randn(experts, width, ff, device=device) * 0.02).to(dtype)
+        gin = torch.zeros(t128 * 128, width, dtype=dtype, device=device)
+        both = torch.zeros(t128 * 128, 2 * ff, device=device)
+        gact = torch.zeros(t128 * 128, ff, dtype=dtype, device=device)
+        gy = torch.zeros(t128 * 128, width, device=device)
+        mem("moe_gather (shared with the like)", time_kernel(lambda: ops.moe_gather(h_in, rows128, texp128, 128, gin, rows_per_input=top), flush),
+            t * top * width * 2 * isz)
+        flop("moe_linear_tc gate and up (tcgen05, 32-bit sums out)", time_kernel(lambda: ops.moe_linear_tc(gin, w_up, texp128, both), flush),
+             2.0 * t * top * 2 * ff * width)
+        mem("silu_mul from 32-bit sums (gated experts)", time_kernel(lambda: ops.silu_mul(both, gact, ff, consume=True, act="silu"), flush),
+            t128 * 128 * ff * (16 + isz))
+        flop("moe_linear_tc down (tcgen05; shared with the like)", time_kernel(lambda: ops.moe_linear_tc(gact, w_down, texp128, gy), flush),
+             2.0 * t * top * ff * width)
+        w_like = (torch.randn(experts, ff, width, device=device) * 0.02).to(dtype)
+        flop("moe_linear_tc up + gelu (like)", time_kernel(lambda: ops.moe_linear_tc(gin, w_like, texp128, gact, gelu=True), flush),
+             2.0 * t * top * ff * width)
+    return out
+
+
 def design_run(args, dtype, device, pk):
     import gc
     import torch
@@ -730,17 +956,24 @@ def design_run(args, dtype, device, pk):
              "zozenex": "width 2048, vocabulary 32000; retention 16 heads, keys of 64, values of 128; every fourth layer window "
                         "attention (16 heads, 4 key/value heads, keys of 64, values of 128, window 1024, blocks of 64) beside gated "
                         "linear attention (8 heads, keys of 64, values of 128, rank 16); 32 experts of 1408, 4 chosen, a shared "
-                        "expert of 1408; beside: the Dunelix model of --design dunelix at equal width, layers and vocabulary"}
+                        "expert of 1408; beside: the Dunelix model of --design dunelix at equal width, layers and vocabulary",
+             "fiponex": "width 2048, vocabulary 32000; layers in turn: gated delta rule (16 heads, 8 query/key heads, keys and values "
+                        "of 128, 4 taps) + dense gated feed-forward of 5632; the same + 32 gated experts of 1408, 4 chosen; latent "
+                        "attention (16 heads, 64 plain + 64 rotated, values of 128, latent 192, window 1024) + experts; attention "
+                        "with a sink (16 heads, 4 key/value heads, keys and values of 128, gate per value) + dense; beside: the "
+                        "Zozenex model of --design zozenex at equal width, layers and vocabulary"}
     result = {"design": args.design, "dtype": args.dtype, "layers": DESIGN_LAYERS, "peaks": pk["source"],
               "sizes": sizes[args.design],
               "l2": "whole steps: weights larger than L2; kernels alone: L2 flushed before every timed call"}
     sampler = ClockSampler().start()
-    labels = ("dunelix", "llama") if args.design == "dunelix" else ("zozenex", "dunelix")
+    labels = {"dunelix": ("dunelix", "llama"), "zozenex": ("zozenex", "dunelix"), "fiponex": ("fiponex", "zozenex")}[args.design]
     for label in labels[:1 if args.only == "decode" else 2]:
         if label == "dunelix":
             cfg, model = build_design(dunelix_shape(), dtype, device)
         elif label == "zozenex":
             cfg, model = build_design(zozenex_shape(), dtype, device)
+        elif label == "fiponex":
+            cfg, model = build_design(fiponex_shape(), dtype, device)
         else:
             cfg, model = build_model(DESIGN_LAYERS, dtype, device)
         runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
@@ -753,6 +986,7 @@ def design_run(args, dtype, device, pk):
             ms, launched, ctx = timed_decode(runner, bsz, CONTEXT - (REPEATS * steps + warmup), steps, warmup, out, repeats=REPEATS)
             moved = design_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "dunelix" else \
                 zozenex_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "zozenex" else \
+                fiponex_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "fiponex" else \
                 decode_bytes(model, runner, bsz, ctx, itemsize)
             rec[f"decode_b{bsz}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(bsz * 1e3 / ms, 1),
                                      "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "gpu_launches": launched}
@@ -762,7 +996,7 @@ def design_run(args, dtype, device, pk):
         torch.cuda.empty_cache()
     result["clocks"] = sampler.stop()
     if dtype == torch.bfloat16 and args.only == "all":
-        result["kernels"] = (design_kernels if args.design == "dunelix" else zozenex_kernels)(dtype, device, pk)
+        result["kernels"] = {"dunelix": design_kernels, "zozenex": zozenex_kernels, "fiponex": fiponex_kernels}[args.design](dtype, device, pk)
     ops.check_status()
     print(json.dumps(result))
     return 0
@@ -787,7 +1021,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
-    ap.add_argument("--design", default=None, choices=["dunelix", "zozenex"],
+    ap.add_argument("--design", default=None, choices=["dunelix", "zozenex", "fiponex"],
                     help="instead of the flagship run: this design's prefill and decode at real layer sizes beside the Llama "
                          "decoder at equal sizes, and its kernels beside their like kernels (one plain line, no record)")
     ap.add_argument("--quick", action="store_true",

@@ -164,6 +164,31 @@ def test_latent_norm_pairwise_rotation_and_cache_write(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_one_product_per_head_in_one_launch(dtype):
+    """Heads side by side in wider rows, inputs and outputs at offsets of their own; sizes the tensor-core tiles take
+    and sizes they do not (odd K, odd offsets), one token and several row tiles; a row's bits do not depend on the
+    rows beside it."""
+    from tiny_llm_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    for t, heads, k, n, a_pad, o_pad, a_off in [(1, 3, 16, 24, 8, 4, 0), (130, 2, 64, 192, 32, 0, 8), (70, 5, 6, 18, 10, 3, 1),
+                                                (9, 1, 9, 7, 0, 0, 0), (33, 4, 40, 100, 2, 6, 2)]:
+        wide = torch.randn(t, a_off + heads * (k + a_pad) + 6, generator=g).to(dtype).to(DEV)
+        a = wide[:, a_off:a_off + heads * (k + a_pad)].view(t, heads, k + a_pad)[:, :, :k]
+        w = (torch.randn(heads, n, k, generator=g) * 0.3).to(dtype).to(DEV)
+        ref = torch.einsum("thk,hnk->thn", a.double().cpu(), w.double().cpu())
+        for out_dtype in {dtype, torch.float32}:
+            full = torch.full((t, heads, n + o_pad), 7.0, dtype=out_dtype, device=DEV)
+            ops.head_linear(a, w, full[:, :, :n])
+            close(full[:, :, :n], ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32,
+                  f32=2e-5 if dtype == torch.float32 else 1e-5, what=f"{heads} products of {k} -> {n}")
+            if o_pad:
+                assert float((full[:, :, n:].float() - 7.0).abs().max()) == 0.0      # nothing written beside the outputs
+            alone = torch.empty(1, heads, n, dtype=out_dtype, device=DEV)
+            ops.head_linear(a[t - 1:], w, alone)
+            assert torch.equal(alone[0], full[t - 1, :, :n])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_sigmoid_gates_per_value_and_per_head(dtype):
     from tiny_llm_b200 import ops
     g = torch.Generator().manual_seed(7)

@@ -737,6 +737,24 @@ def latent_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int,
           t, _code(proj.dtype), _stream())
 
 
+def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """One small product per head in one launch: out[t, h, :] = w[h] . a[t, h, :].  a [T, heads, K] and out
+    [T, heads, N] are views whose last dimension is contiguous (rows of tokens with the heads side by side, at any
+    row stride and any distance between heads); w [heads, N, K] contiguous, of a's dtype; out of a's dtype or float32.
+    bfloat16 with even K and even offsets runs on mma.sync tiles read straight from global memory, everything else
+    on FFMA tiles; either way an output's sum runs over ascending k whatever else is in the batch."""
+    _need_cuda(a, w, out)
+    t, heads, k = a.shape
+    n = w.shape[1]
+    if w.shape != (heads, n, k) or not w.is_contiguous() or w.dtype != a.dtype or out.shape != (t, heads, n) or \
+            a.stride(2) != 1 or out.stride(2) != 1 or out.dtype not in (a.dtype, torch.float32):
+        raise KernelError("head_linear: shapes or dtypes do not fit")
+    lib = build.load_library("head_linear")
+    ll = ctypes.c_longlong
+    _call(lib, lib.tllm_head_linear, _ptr(a), ll(a.stride(0)), a.stride(1), _ptr(w), _ptr(out), ll(out.stride(0)),
+          out.stride(1), t, heads, n, k, _code(a.dtype), _code(out.dtype), 0 if force_generic else 1, _stream())
+
+
 def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, value_dim: int, out: torch.Tensor) -> None:
     """out[t, h, :] = x[t, h, :] * sigmoid(gate[t, ...]): `gate` [T, heads * value_dim] gates every value, `gate`
     [T, heads] every head as a whole.  x float32, gate (a row slice is fine) and out in the engine's dtype."""
@@ -1317,12 +1335,12 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
 
 
 ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "attention_prep", "recurrence",
-                 "linear_attention", "delta_rule", "window_attention", "moe", "sampling")
+                 "linear_attention", "delta_rule", "head_linear", "window_attention", "moe", "sampling")
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use
 ATTENTION_TC_HEAD_DIMS = (64, 128)            # head sizes the tcgen05 prompt-attention kernel is written for
-ATTENTION_MAPS_DIMS = ((64, 128),)            # (key size, value size) pairs of the multi-map kernel compiled ahead
+ATTENTION_MAPS_DIMS = ((64, 128), (128, 128), (256, 192))           # (key size, value size) pairs of the multi-map kernel compiled ahead
 
 
 WINDOW_ATTENTION_DIMS = ((64, 128),)   # (key size, value size) pairs of the window attention built ahead; others on first use

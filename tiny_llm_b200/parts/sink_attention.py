@@ -158,9 +158,9 @@ class LatentAttention:
         self.w_sink = weights[prefix + "sink"] if self.sink else None
         uk, uv = weights[prefix + "uk"], weights[prefix + "uv"]
         # per head: the keys' up-projection transposed (it takes the plain query part into the latent's space) and
-        # the values' up-projection as it is
-        self.w_uk_t = [uk[i * nd:(i + 1) * nd].t().contiguous() for i in range(nh)]
-        self.w_uv = [uv[i * vd:(i + 1) * vd].contiguous() for i in range(nh)]
+        # the values' up-projection as it is, each stacked [heads, outputs, inputs] for the per-head product
+        self.w_uk_t = uk.view(nh, nd, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = uv.view(nh, vd, self.rank).contiguous()
         self.freq = pair_frequencies(self.rot_dims, self.rot_base).to(self.w_o.device) if self.rot_dims else None
 
     def forward(self, ctx, h, resid, cache) -> None:
@@ -173,16 +173,14 @@ class LatentAttention:
         q_lat = ctx.workspace.get("latent_q", (t, nh, kd), ctx.dtype)
         ops.latent_kv_write(proj, ctx.batch.positions, nh, nd, rd, rank, self.rot_dims, self.freq, self.w_norm, self.eps,
                             q_lat, cache.k, cache.v, cache.slot_mapping)
-        for i in range(nh):
-            ops.linear(proj[:, i * qd:i * qd + nd], self.w_uk_t[i], q_lat[:, i, :rank])
+        ops.head_linear(proj[:, :nh * qd].view(t, nh, qd)[:, :, :nd], self.w_uk_t, q_lat[:, :, :rank])
         attn = ctx.workspace.get("attn_maps", (t, nh * rank), torch.float32)
         ops.paged_attention_maps(q_lat.view(t, nh * kd), nh, 1, 1, kd, rank, cache.k, cache.v, cache.block_table,
                                  ctx.batch, attn, self.scale, self.window, None, sink=self.w_sink)
         gated = ctx.workspace.get("latent_o", (t, nh * rank), ctx.dtype)
         ops.sigmoid_gate(attn, proj[:, self.q_dim + kd:self.q_dim + kd + nh], nh, rank, gated)
         out = ctx.workspace.get("attn_out", (t, nh * vd), ctx.dtype)
-        for i in range(nh):
-            ops.linear(gated[:, i * rank:(i + 1) * rank], self.w_uv[i], out[:, i * vd:(i + 1) * vd])
+        ops.head_linear(gated.view(t, nh, rank), self.w_uv, out.view(t, nh, vd))
         ops.linear(out, self.w_o, resid, accumulate=True)
 
 
