@@ -848,13 +848,9 @@ def fiponex_kernels(dtype, device, pk, tokens=2048):
     wl = torch.ones(rank, device=device)
     mem("latent_kv_write (norm, pair rotation)", time_kernel(lambda: ops.latent_kv_write(
         lproj, pos, h, nd, rd, rank, rd, freq, wl, 1e-6, q_lat, lkc, lvc, slots), flush), t * isz * (h * rd * 2 + lkd * 2 + rank))
-    w_uk_t = [rnd(rank, nd) for _ in range(h)]
-    w_uv = [rnd(lvd, rank) for _ in range(h)]
-
-    def absorb():
-        for i in range(h):
-            ops.linear(lproj[:, i * (nd + rd):i * (nd + rd) + nd], w_uk_t[i], q_lat[:, i, :rank])
-    flop("latent query products (16 heads, 64 -> 192)", time_kernel(absorb, flush), 2.0 * t * h * nd * rank)
+    w_uk_t, w_uv = rnd(h, rank, nd), rnd(h, lvd, rank)
+    flop("head_linear: latent query products (16 heads, 64 -> 192)", time_kernel(lambda: ops.head_linear(
+        lproj[:, :h * (nd + rd)].view(t, h, nd + rd)[:, :, :nd], w_uk_t, q_lat[:, :, :rank]), flush), 2.0 * t * h * nd * rank)
     latt = torch.empty(t, h * rank, dtype=torch.float32, device=device)
     wpairs = sum(min(p + 1, window) for p in range(t))
     flop("latent attention (16 heads, key row 256, value row 192, window 1024)", time_kernel(lambda: ops.paged_attention_maps(
@@ -865,10 +861,8 @@ def fiponex_kernels(dtype, device, pk, tokens=2048):
         t * h * rank * (4 + isz))
     lout = torch.empty(t, h * lvd, dtype=dtype, device=device)
 
-    def values_up():
-        for i in range(h):
-            ops.linear(lg[:, i * rank:(i + 1) * rank], w_uv[i], lout[:, i * lvd:(i + 1) * lvd])
-    flop("latent value products (16 heads, 192 -> 128)", time_kernel(values_up, flush), 2.0 * t * h * rank * lvd)
+    flop("head_linear: latent value products (16 heads, 192 -> 128)", time_kernel(lambda: ops.head_linear(
+        lg.view(t, h, rank), w_uv, lout.view(t, h, lvd)), flush), 2.0 * t * h * rank * lvd)
     # like: the Zozenex window attention with its rotation kernel, the Dunelix attention with two maps
     zh, zkv, zkd, zvd, pool = 16, 4, 64, 128, 64
     zq = rnd(t, (zh + zkv) * zkd + zkv * zvd)
@@ -932,8 +926,8 @@ def fiponex_kernels(dtype, device, pk, tokens=2048):
             t * top * width * 2 * isz)
         flop("moe_linear_tc gate and up (tcgen05, 32-bit sums out)", time_kernel(lambda: ops.moe_linear_tc(gin, w_up, texp128, both), flush),
              2.0 * t * top * 2 * ff * width)
-        mem("silu_mul from 32-bit sums (gated experts)", time_kernel(lambda: ops.silu_mul(both, gact, ff, consume=True, act="silu"), flush),
-            t128 * 128 * ff * (16 + isz))
+        mem("silu_mul from 32-bit sums (gated experts)", time_kernel(lambda: ops.silu_mul(both, gact, ff, act="silu"), flush),
+            t128 * 128 * ff * (8 + isz))
         flop("moe_linear_tc down (tcgen05; shared with the like)", time_kernel(lambda: ops.moe_linear_tc(gact, w_down, texp128, gy), flush),
              2.0 * t * top * ff * width)
         w_like = (torch.randn(experts, ff, width, device=device) * 0.02).to(dtype)

@@ -12,7 +12,7 @@ from fiponex_util import FIP, compare, plain_logits, plain_model, tolerances, wr
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 LENGTHS = {"A": [100, 64, 33, 47, 130, 17, 2, 51], "B": [97, 1, 40, 200, 33, 64, 13, 150], "C": [70, 90, 35, 49, 8],
-           "D": [61, 5, 44, 90, 23]}
+           "D": [61, 5, 44, 90, 23], "E": [300, 131, 70, 260, 9]}
 
 
 @pytest.fixture(scope="module")
@@ -39,7 +39,7 @@ def runner_for(model_dir, dtype, page, max_tokens, max_requests=4, poison=True, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("how", ["whole", "tail", "portions", "mixed"])
 def test_replay_in_process(cases, name, dtype, how):
     model_dir, cfg, page, reqs, ref, tol = cases[name]
@@ -54,7 +54,7 @@ def test_replay_in_process(cases, name, dtype, how):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "E"])
 def test_trace_run_program(cases, name, dtype):
     """All four ways of cutting, through bin/trace_run as a user runs it, with the smallest pool and four slots."""
     model_dir, cfg, page, reqs, ref, tol = cases[name]
@@ -82,7 +82,7 @@ def test_prompt_portions_through_the_tcgen05_grouped_product(cases, name, monkey
     ops.check_status()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_cuts_batches_and_pages_do_not_move_the_32_bit_logits(cases, name):
     """Whole, portions, and mixed batches with other page sizes and pools: the 32-bit path gives the same bits."""
     model_dir, cfg, page, reqs, ref, tol = cases[name]

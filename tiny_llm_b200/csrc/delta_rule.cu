@@ -12,7 +12,7 @@
 //   g = exp(-exp(A_log) softplus(a + dt_bias)), beta = sigmoid(b).  All outputs float32.
 // conv_state_update: the state's kept inputs after the step: the last taps - 1 of (kept inputs ++ the step's).
 // delta_rule_scan: a group of 8 lanes owns one value column of one (request, head): the column's state rows lie in
-//   the lanes' registers (row = i * 8 + lane of the group).  Per token one round of shuffles gives the column's
+//   the lanes' registers (a lane holds R consecutive rows).  Per token one round of shuffles gives the column's
 //   S^T k, S^T q and k . q from the state as it was; with those
 //       u = beta (v - g S^T k),   o = g S^T q + u (k . q),   S <- g S + k u
 //   which is the sequence above with the read-out written in terms of the old state.  Tokens are staged in shared
@@ -136,15 +136,24 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int R>   // state rows per lane: R * DR_LANES >= key size
+template <int R>   // state rows per lane, a multiple of 4: R * DR_LANES >= key size
 __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
-  constexpr int KP = R * DR_LANES;
+  // A lane owns R consecutive state rows of its column (rows sub * R ... sub * R + R - 1), so that its part of a key
+  // or query is read from shared memory in 16-byte pieces; a lane's part lies R + 4 floats from the next lane's, which
+  // spreads the eight lanes of a column over all banks.
+  constexpr int CH = R + 4;
+  constexpr int KP = CH * DR_LANES;
   // per stage: q and k of DR_TOK tokens (rows past the key size stay zero), their values of this CTA's columns,
   // decay and step size
-  __shared__ float sq[2][DR_TOK][KP], sk[2][DR_TOK][KP], sv[2][DR_TOK][DR_COLS], sg[2][DR_TOK][2];
+  __shared__ __align__(16) float sq[2][DR_TOK][KP], sk[2][DR_TOK][KP];
+  __shared__ float sv[2][DR_TOK][DR_COLS], sg[2][DR_TOK][2];
   pdl_trigger();
   const int tid = threadIdx.x;
   const int sub = tid & (DR_LANES - 1), cl = tid / DR_LANES;
@@ -160,17 +169,32 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   float s[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int row = i * DR_LANES + sub;
+    const int row = sub * R + i;
     s[i] = (col_ok && row < a.kd) ? st[row] : 0.f;
   }
   __syncthreads();   // the zeros are in place before any copy lands beside them
   const int qk_ld = a.kv_heads * a.kd, v_ld = a.heads * a.vd;
+  // 16-byte copies when a key row is made of whole pieces that start on 16-byte boundaries
+  const bool wide = (a.kd & 3) == 0 && ((((size_t)a.q) | ((size_t)a.k)) & 15) == 0;
   auto stage = [&](int buf, int tb) {
     const int nt = min(DR_TOK, t1 - tb);
-    for (int i = tid; i < nt * a.kd; i += 128) {
-      const int tt = i / a.kd, d = i % a.kd;
-      cp_async4(&sq[buf][tt][d], a.q + (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d);
-      cp_async4(&sk[buf][tt][d], a.k + (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d);
+    if (wide) {
+      const int per = a.kd >> 2;
+      for (int i = tid; i < nt * per; i += 128) {
+        const int tt = i / per, d = (i - tt * per) << 2;
+        const int at = (d / R) * CH + d % R;
+        const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
+        cp_async16(&sq[buf][tt][at], a.q + src);
+        cp_async16(&sk[buf][tt][at], a.k + src);
+      }
+    } else {
+      for (int i = tid; i < nt * a.kd; i += 128) {
+        const int tt = i / a.kd, d = i - tt * a.kd;
+        const int at = (d / R) * CH + d % R;
+        const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
+        cp_async4(&sq[buf][tt][at], a.q + src);
+        cp_async4(&sk[buf][tt][at], a.k + src);
+      }
     }
     for (int i = tid; i < nt * DR_COLS; i += 128) {
       const int tt = i / DR_COLS, c = i % DR_COLS;
@@ -179,6 +203,15 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
     }
     for (int i = tid; i < nt * 2; i += 128)
       cp_async4(&sg[buf][i / 2][i % 2], a.gb + ((size_t)(tb + i / 2) * a.heads + h) * 2 + i % 2);
+  };
+  auto fetch = [&](int buf, int tt, float* kr, float* qr) {   // this lane's part of a staged token's key and query
+#pragma unroll
+    for (int i = 0; i < R; i += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(&sk[buf][tt][sub * CH + i]);
+      const float4 qv = *reinterpret_cast<const float4*>(&sq[buf][tt][sub * CH + i]);
+      kr[i] = kv.x; kr[i + 1] = kv.y; kr[i + 2] = kv.z; kr[i + 3] = kv.w;
+      qr[i] = qv.x; qr[i + 1] = qv.y; qr[i + 2] = qv.z; qr[i + 3] = qv.w;
+    }
   };
   stage(0, t0);
   cp_commit();
@@ -189,29 +222,42 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
     cp_wait<1>();
     __syncthreads();
     const int nt = min(DR_TOK, t1 - tb);
-    for (int tt = 0; tt < nt; ++tt) {
-      float pa = 0.f, pb = 0.f, pc = 0.f;
-      float kr[R];
+    float kn[R], qn[R];
+    fetch(buf, 0, kn, qn);
+    auto token = [&](int tt, bool more) {
+      float kr[R], qr[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) { kr[i] = kn[i]; qr[i] = qn[i]; }
+      if (more) fetch(buf, tt + 1, kn, qn);   // the next token's parts are on their way during this token's sums
+      // four partial sums each, rows i, i + 4, i + 8, ... in one of them: short chains of dependent operations
+      float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f}, pc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        kr[i] = sk[buf][tt][i * DR_LANES + sub];
-        const float qr = sq[buf][tt][i * DR_LANES + sub];
-        pa = fmaf(s[i], kr[i], pa);
-        pb = fmaf(s[i], qr, pb);
-        pc = fmaf(kr[i], qr, pc);
+        pa[i & 3] = fmaf(s[i], kr[i], pa[i & 3]);
+        pb[i & 3] = fmaf(s[i], qr[i], pb[i & 3]);
+        pc[i & 3] = fmaf(kr[i], qr[i], pc[i & 3]);
       }
+      float xa = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+      float xb = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+      float xc = (pc[0] + pc[1]) + (pc[2] + pc[3]);
 #pragma unroll
       for (int o = DR_LANES / 2; o > 0; o >>= 1) {
-        pa += __shfl_xor_sync(0xffffffffu, pa, o);
-        pb += __shfl_xor_sync(0xffffffffu, pb, o);
-        pc += __shfl_xor_sync(0xffffffffu, pc, o);
+        xa += __shfl_xor_sync(0xffffffffu, xa, o);
+        xb += __shfl_xor_sync(0xffffffffu, xb, o);
+        xc += __shfl_xor_sync(0xffffffffu, xc, o);
       }
       const float g = sg[buf][tt][0], beta = sg[buf][tt][1];
-      const float u = __fmul_rn(beta, fmaf(-g, pa, sv[buf][tt][cl]));
-      const float o = fmaf(u, pc, __fmul_rn(g, pb));
+      const float u = __fmul_rn(beta, fmaf(-g, xa, sv[buf][tt][cl]));
+      const float o = fmaf(u, xc, __fmul_rn(g, xb));
 #pragma unroll
       for (int i = 0; i < R; ++i) s[i] = fmaf(kr[i], u, __fmul_rn(g, s[i]));
       if (sub == 0 && col_ok) a.out[(size_t)(tb + tt) * v_ld + (size_t)h * a.vd + col] = o;
+    };
+    if (nt == DR_TOK) {   // a whole stage: unrolled, so that loads of later tokens can move ahead of earlier sums
+#pragma unroll
+      for (int tt = 0; tt < DR_TOK; ++tt) token(tt, tt + 1 < DR_TOK);
+    } else {
+      for (int tt = 0; tt < nt; ++tt) token(tt, tt + 1 < nt);
     }
     __syncthreads();   // the stage is free for the copies after the next
   }
@@ -219,7 +265,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   if (col_ok) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int row = i * DR_LANES + sub;
+      const int row = sub * R + i;
       if (row < a.kd) st[row] = s[i];
     }
   }

@@ -142,6 +142,40 @@ __global__ void silu_mul_kernel(TIn* __restrict__ gu, TOut* __restrict__ out, in
   }
 }
 
+// The same from float32 sums, four neighbouring outputs per thread (the block and the row are multiples of four values
+// and the rows 16-byte aligned): two 16-byte loads, one store.  ZERO hands the sums back cleared.
+template <typename TOut, bool ZERO>
+__global__ void __launch_bounds__(256) silu_mul_f32x4_kernel(float* __restrict__ gu, TOut* __restrict__ out, int m, int inter,
+                                                             int blk, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int per_row = inter >> 2;
+  const long long total = (long long)m * per_row;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(idx / per_row), col = (int)(idx - (long long)row * per_row) << 2;
+    const int g = col / blk, j = col - g * blk;
+    float* src = gu + (size_t)row * 2 * inter + (size_t)g * 2 * blk + j;
+    const float4 gate = *reinterpret_cast<const float4*>(src), up = *reinterpret_cast<const float4*>(src + blk);
+    if (ZERO) {
+      *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(src + blk) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float gv[4] = {gate.x, gate.y, gate.z, gate.w}, uv[4] = {up.x, up.y, up.z, up.w};
+    float r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = (act == 1 ? fmaxf(gv[i], 0.f) : gv[i] / (1.f + expf(-gv[i]))) * uv[i];
+    TOut* dst = out + (size_t)row * inter + col;
+    if constexpr (sizeof(TOut) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = pk;
+    } else {
+      *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- rotate and cache
 // qkv row: [nq*hd queries | nkv*hd keys | nkv*hd values] (keys/values absent when slot_mapping is
 // null).  Queries are rotated in place; keys are rotated and written to the key pages, values are
@@ -588,12 +622,25 @@ extern "C" int tllm_silu_mul(void* gu, void* out, int m, int inter, int blk, int
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   cudaStream_t s = (cudaStream_t)stream;
+  if (in_dtype == TLLM_F32 && blk % 4 == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0 && (out_dtype == TLLM_F32 || out_dtype == TLLM_BF16)) {
+    const size_t quads = total / 4;
+    const int vblocks = (int)((quads + threads - 1) / threads < 148 * 16 ? (quads + threads - 1) / threads : 148 * 16);
+    if (out_dtype == TLLM_F32 && zero_src) TLLM_LAUNCH("silu_mul", (silu_mul_f32x4_kernel<float, true>), vblocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk, act);
+    else if (out_dtype == TLLM_F32) TLLM_LAUNCH("silu_mul", (silu_mul_f32x4_kernel<float, false>), vblocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk, act);
+    else if (zero_src) TLLM_LAUNCH("silu_mul", (silu_mul_f32x4_kernel<__nv_bfloat16, true>), vblocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
+    else TLLM_LAUNCH("silu_mul", (silu_mul_f32x4_kernel<__nv_bfloat16, false>), vblocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
+    return TLLM_OK;
+  }
   if (in_dtype == TLLM_F32 && out_dtype == TLLM_F32 && !zero_src)
     TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, float, false>), blocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk, act);
   else if (in_dtype == TLLM_BF16 && out_dtype == TLLM_BF16 && !zero_src)
     TLLM_LAUNCH("silu_mul", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16, false>), blocks, threads, 0, s, (__nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
   else if (in_dtype == TLLM_F32 && out_dtype == TLLM_BF16 && zero_src)
     TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, __nv_bfloat16, true>), blocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
+  else if (in_dtype == TLLM_F32 && out_dtype == TLLM_BF16 && !zero_src)
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, __nv_bfloat16, false>), blocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk, act);
+  else if (in_dtype == TLLM_F32 && out_dtype == TLLM_F32 && zero_src)
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, float, true>), blocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk, act);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "silu_mul: dtype codes %d -> %d with zero_src %d are not built", in_dtype, out_dtype, zero_src);
   return TLLM_OK;

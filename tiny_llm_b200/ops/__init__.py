@@ -262,11 +262,12 @@ GLU_ACTS = {"silu": 0, "relu": 1}
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False, act: str = "silu") -> None:
     """out[m, g*block + j] = act(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j], act = silu or relu.
-    consume=True: `gate_up` is a float32 accumulation buffer (split-K sums) and is handed back zeroed."""
+    `gate_up` is of out's dtype or float32 (a product's 32-bit sums).  consume=True: `gate_up` is a float32
+    accumulation buffer (split-K sums) and is handed back zeroed."""
     _need_cuda(gate_up, out)
     m, inter = out.shape
     if gate_up.shape != (m, 2 * inter) or not gate_up.is_contiguous() or not out.is_contiguous() or \
-            (consume and gate_up.dtype != torch.float32) or (not consume and gate_up.dtype != out.dtype):
+            (consume and gate_up.dtype != torch.float32) or (not consume and gate_up.dtype not in (out.dtype, torch.float32)):
         raise KernelError("silu_mul: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
     if act not in GLU_ACTS:

@@ -103,7 +103,7 @@ class RoutedExperts:
             if glu is not None:
                 both = ws.get("moe_gate_up", (tiles * tile, up_rows), torch.float32)
                 ops.moe_linear_tc(grouped_in, self.w_up, tile_expert, both)
-                ops.silu_mul(both, act, f, consume=True, act=glu)
+                ops.silu_mul(both, act, f, act=glu)     # the product stores its sums: nothing to hand back zeroed
             else:
                 ops.moe_linear_tc(grouped_in, self.w_up, tile_expert, act, gelu=True)
             y = ws.get("moe_y", (tiles * tile, self.hidden_size), torch.float32)
