@@ -77,14 +77,14 @@ FIP_D = model(97, 40, 2.0, 1e-5, 0.12, [
 # experts' scores closer than bfloat16 rounding, and which of the two is taken is not what this configuration is for.
 FIP_E = model(257, 128, 11.3, 1e-6, 0.05, [
     attention(8, 1, 80, 48, 0.11, q_temp=(0.5, 64), mlp=moe(5, 5, 32)),
-    latent(8, 32, 16, 48, 64, 0.15, size=150, rot=(16, 500000.0), mlp=dense(160)),
+    latent(8, 32, 16, 48, 64, 0.15, size=150, rot=(16, 250000.0), mlp=dense(160)),
     delta(8, 2, 48, 32, 4, mlp=moe(4, 4, 48)),
     attention(10, 2, 16, 64, 0.25, mlp=dense(96)),
     delta(2, 2, 64, 96, 3, mlp=dense(64)),
     latent(4, 48, 32, 16, 96, 0.1, size=129, rot=(32, 10000.0), mlp=moe(8, 8, 16)),
     attention(2, 2, 128, 128, 0.09, q_temp=(0.2, 100), mlp=None),
 ])
-FIP = {"A": (FIP_A, 16, 3), "B": (FIP_B, 8, 4), "C": (FIP_C, 4, 5), "D": (FIP_D, 4, 6), "E": (FIP_E, 32, 8)}   # config, page size, seed
+FIP = {"A": (FIP_A, 16, 3), "B": (FIP_B, 8, 4), "C": (FIP_C, 4, 5), "D": (FIP_D, 4, 6), "E": (FIP_E, 32, 9)}   # config, page size, seed
 
 
 def write_models(tmp_path_factory):

@@ -474,7 +474,7 @@ class ModelRunner:
         if len(self._tapes) >= self.MAX_TAPES:
             self._tapes.pop(next(iter(self._tapes)))     # the oldest
         # the tape's launches point into these buffers: keep them alive even if the workspace grows
-        self._tapes[key] = (tape, logits, list(self.workspace._buffers.values()))
+        self._tapes[key] = (tape, logits, self.workspace.buffers())
         return logits
 
     def _run(self, entries, batch: StepBatch):
@@ -496,7 +496,7 @@ class ModelRunner:
             kernels = ops.launches - before
             ops.launches = before
             # the graph's launches point into these buffers: keep them alive even if the workspace grows
-            held = (graph, logits, list(self.workspace._buffers.values()), kernels)
+            held = (graph, logits, self.workspace.buffers(), kernels)
             self._graphs[key] = held
         held[0].replay()
         ops.launches += held[3]

@@ -2,7 +2,7 @@
 name (or as `reserve` made it), so the addresses stay put once the engine is warm."""
 from __future__ import annotations
 
-from typing import Dict, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
@@ -12,7 +12,22 @@ class Workspace:
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._views: Dict[tuple, torch.Tensor] = {}    # (name, dtype, shape) -> the view handed out before
+        # Buffers that a larger one replaced.  A launch noted on a tape (or captured in a graph) may point into one
+        # that was replaced later in the very step that noted it, when a second user of the name asked for more:
+        # they stay allocated, so that no tape ever points into memory that something else was given since.
+        self._retired: List[torch.Tensor] = []
         self.frozen = False
+
+    def buffers(self) -> List[torch.Tensor]:
+        """Every buffer that a launch made so far can point into: the current ones and the replaced ones."""
+        return list(self._buffers.values()) + list(self._retired)
+
+    def _replace(self, key, new: torch.Tensor) -> None:
+        old = self._buffers.get(key)
+        if old is not None:
+            self._retired.append(old)
+        self._buffers[key] = new
+        self._drop_views(key)
 
     def reserve(self, name: str, numel: int, dtype: torch.dtype) -> None:
         key = (name, dtype)
@@ -21,8 +36,7 @@ class Workspace:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow to {numel} elements "
                                    f"while its address is pinned by a captured graph")
-            self._buffers[key] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
-            self._drop_views(key)
+            self._replace(key, torch.empty(max(numel, 1), dtype=dtype, device=self.device))
 
     def _drop_views(self, key) -> None:
         for k in [k for k in self._views if k[0] == key[0] and k[1] == key[1]]:
@@ -54,6 +68,5 @@ class Workspace:
         if cur is None or cur.numel() < numel:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while its address is pinned")
-            self._buffers[key] = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
-            self._drop_views(key)
+            self._replace(key, torch.zeros(max(numel, 1), dtype=dtype, device=self.device))
         return self._buffers[key][:numel].view(*shape)
