@@ -194,3 +194,21 @@ def test_plain_model_prefill_does_not_depend_on_later_tokens():
         toks = torch.randint(0, cfg["vocab"], (50,), generator=torch.Generator().manual_seed(1)).tolist()
         whole = pf.forward(c, w, toks)
         assert float((pf.forward(c, w, toks[:31]) - whole[:31]).abs().max()) < 1e-9
+
+
+def test_a_replaced_workspace_buffer_stays_allocated():
+    """Layers of unequal widths ask for one name with growing sizes inside one step; launches noted before the
+    growth point into the smaller buffer, which must not be given to anything else while a tape can be replayed."""
+    from tiny_llm_b200.engine import Workspace
+    ws = Workspace(torch.device("cpu"))
+    small = ws.get("rows", (3, 8), torch.float32)
+    small.fill_(7.0)
+    zeroed = ws.get_zeroed("sums", (3, 4))
+    large = ws.get("rows", (3, 32), torch.float32)
+    more = ws.get_zeroed("sums", (5, 4))
+    assert large.data_ptr() != small.data_ptr() and more.data_ptr() != zeroed.data_ptr()
+    held = {b.data_ptr() for b in ws.buffers()}
+    assert {small.data_ptr(), large.data_ptr(), zeroed.data_ptr(), more.data_ptr()} <= held
+    assert float(small.min()) == 7.0 and float(more.abs().max()) == 0.0
+    assert ws.get("rows", (3, 32), torch.float32).data_ptr() == large.data_ptr()      # no growth: the same address
+    assert ws.get("rows", (2, 8), torch.float32).data_ptr() == large.data_ptr()
