@@ -294,6 +294,34 @@ def test_sink_attention_sees_exactly_the_window_and_finds_a_planted_key(dtype, w
         assert float((same_type - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("kd,vd,heads,kvh,window", [(16, 32, 4, 2, None), (128, 96, 6, 1, 150), (80, 48, 8, 1, None), (32, 16, 5, 5, 200)])
+def test_decoded_tokens_with_the_keys_in_runs_match_one_run(kd, vd, heads, kvh, window):
+    """A step of decoded tokens may walk a row tile's keys in several runs that a second kernel joins: the same
+    softmax (sink included) up to 32-bit rounding, for contexts of one token, of less than a tile, and of many tiles,
+    with runs that end up empty for the short ones."""
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import Workspace
+    g = torch.Generator().manual_seed(17)
+    page, contexts = 16, [1, 40, 300, 700, 65]
+    r = len(contexts)
+    pages_per = -(-max(contexts) // page)
+    table = torch.arange(r * pages_per, dtype=torch.int32).view(r, pages_per)
+    kc = (torch.randn(r * pages_per, kvh, page, kd, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    vc = torch.randn(r * pages_per, kvh, page, vd, generator=g).to(torch.bfloat16).to(DEV)
+    q = torch.randn(r, heads * kd + 8, generator=g).to(torch.bfloat16).to(DEV)
+    sink = torch.randn(heads, generator=g).to(DEV)
+    batch = SimpleNamespace(cu_q=i32(list(range(r + 1))), q_start=i32([c - 1 for c in contexts]), num_requests=r, max_q_len=1,
+                            max_kv_len=1024, token_request=i32(list(range(r))), positions=i32([c - 1 for c in contexts]))
+    one, runs = torch.empty(r, heads * vd, device=DEV), torch.empty(r, heads * vd, device=DEV)
+    for sk in (sink, None):
+        ops.paged_attention_maps(q, heads, kvh, 1, kd, vd, kc, vc, table.to(DEV), batch, one, 0.2, window, None, sink=sk)
+        ws = Workspace(torch.device(DEV))
+        before = ops.launches
+        ops.paged_attention_maps(q, heads, kvh, 1, kd, vd, kc, vc, table.to(DEV), batch, runs, 0.2, window, None, sink=sk, workspace=ws)
+        assert ops.launches - before == 1 and ws.buffers(), "the keys were not cut into runs"
+        assert float((one - runs).abs().max()) <= 4e-6 * max(1.0, float(one.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kd,vd,heads,kvh,window,page", [(16, 32, 4, 2, 24, 8), (48, 32, 6, 1, 150, 16), (128, 96, 6, 1, None, 16),
                                                          (28, 18, 5, 1, 7, 4), (24, 40, 3, 3, 50, 16)])
@@ -392,7 +420,7 @@ def run_delta(ops, proj, w_taps, a_log, dt_bias, heads, kvh, kd, vd, taps, state
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kvh,kd,vd,taps", [(4, 2, 16, 8, 4), (3, 3, 24, 40, 2), (2, 1, 6, 10, 1), (5, 1, 70, 20, 3),
-                                                  (2, 2, 130, 33, 4)])
+                                                  (2, 2, 130, 33, 4), (2, 1, 48, 64, 4), (1, 1, 256, 9, 2), (3, 3, 32, 17, 3)])
 def test_delta_rule_from_a_state_for_unequal_requests(dtype, heads, kvh, kd, vd, taps):
     from tiny_llm_b200 import ops
     g = torch.Generator().manual_seed(heads * kd + vd)
@@ -421,10 +449,10 @@ def test_delta_rule_from_a_state_for_unequal_requests(dtype, heads, kvh, kd, vd,
     assert torch.equal(state_dev[3].cpu(), state[3]) and torch.equal(kept_dev[3].cpu(), kept[3])   # no request's slot
 
 
-def test_delta_rule_in_portions_gives_the_same_bits():
+@pytest.mark.parametrize("heads,kvh,kd,vd,taps,t", [(3, 1, 20, 12, 4, 57), (2, 2, 100, 24, 3, 41), (2, 1, 64, 8, 2, 33)])
+def test_delta_rule_in_portions_gives_the_same_bits(heads, kvh, kd, vd, taps, t):
     from tiny_llm_b200 import ops
     g = torch.Generator().manual_seed(3)
-    heads, kvh, kd, vd, taps, t = 3, 1, 20, 12, 4, 57
     c, proj, w_taps, a_log, dt_bias = delta_inputs(g, t, heads, kvh, kd, vd, taps, torch.float32)
     proj, w_taps, a_log, dt_bias = proj.to(DEV), w_taps.to(DEV), a_log.to(DEV), dt_bias.to(DEV)
 

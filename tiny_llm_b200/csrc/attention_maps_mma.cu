@@ -46,6 +46,10 @@ struct MapsParams {
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
   int q_row_stride, max_blocks, nq, nkv, maps, page_size, window, chunk, tiles_per_req, n_requests;
   float scale_log2;              // scale * log2(e)
+  // Key tiles in `splits` runs (blockIdx.y), for steps of decoded tokens whose grid would not fill the SMs: a run
+  // leaves its rows' unnormalised sums, maximum and denominator in part[run][row][VD + 2]; a second kernel joins them.
+  int splits, total_rows;
+  float* part;
 };
 
 __device__ __forceinline__ int lowest_key(const MapsParams& p, int pos) {
@@ -127,7 +131,12 @@ attention_maps_kernel(const MapsParams p) {
   const int tok_hi = min(q_len - 1, (row0 + BM - 1) / group);
   const int key_hi = start + tok_hi;
   const int key_lo = lowest_key(p, start + tok_lo);    // lowest_key grows with the position
-  const int t_begin = key_lo / BN, t_end = key_hi / BN + 1;   // t_end exclusive
+  int t_begin = key_lo / BN, t_end = key_hi / BN + 1;   // t_end exclusive
+  if (p.splits > 1) {   // this CTA's run of the tiles (possibly empty: its rows then say so with a maximum of -inf)
+    const int per = (t_end - t_begin + p.splits - 1) / p.splits;
+    t_begin = min(t_end, t_begin + (int)blockIdx.y * per);
+    t_end = min(t_end, t_begin + per);
+  }
   const PageLookup pages = stage_pages(table, page_slots, t_begin * BN, t_end * BN, p.page_size, p.max_blocks, threadIdx.x, 128);
   __syncthreads();
 
@@ -277,6 +286,15 @@ attention_maps_kernel(const MapsParams p) {
   for (int half = 0; half < 2; ++half) {
     const int row = half ? r_b : r_a;
     if (row >= rows_total) continue;
+    if (p.splits > 1) {
+      const size_t rid = (size_t)(tok0 + row / group) * p.nq * p.maps + (size_t)((kvh * group + row % group) * p.maps + map);
+      float* dst = p.part + ((size_t)blockIdx.y * p.total_rows + rid) * (VD + 2);
+#pragma unroll
+      for (int i = 0; i < VD / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + t4 * 2) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+      if (t4 == 0) { dst[VD] = half ? m_b : m_a; dst[VD + 1] = half ? l_b : l_a; }
+      continue;
+    }
     float inv = 1.f / (half ? l_b : l_a);
     if (p.sink != nullptr) {   // both terms of the denominator against the larger of the running maximum and the sink
       const float sk = p.sink[kvh * group + row % group] * 1.4426950408889634f, m = half ? m_b : m_a;
@@ -290,6 +308,40 @@ attention_maps_kernel(const MapsParams p) {
   }
 }
 
+// Joins the runs of one row: with M the largest of the runs' maxima (and the sink), out = sum_s o_s 2^(m_s - M) /
+// (sum_s l_s 2^(m_s - M) + 2^(sink - M)), runs in ascending order.  One warp per row.
+__global__ void __launch_bounds__(128) attention_maps_merge_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                                   const float* __restrict__ sink, int total_rows, int splits,
+                                                                   int heads_maps, int maps) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= total_rows) return;
+  constexpr int LD = VD + 2;
+  float top = -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, part[((size_t)s * total_rows + row) * LD + VD]);
+  float extra = 0.f;
+  if (sink != nullptr) {
+    const float sk = sink[(row % heads_maps) / maps] * 1.4426950408889634f;
+    top = fmaxf(top, sk);
+    extra = ex2(sk - top);
+  }
+  float denom = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* src = part + ((size_t)s * total_rows + row) * LD;
+    denom = fmaf(src[VD + 1], ex2(src[VD] - top), denom);     // an empty run: 2^(-inf) = 0
+  }
+  const float inv = 1.f / (denom + extra);
+  for (int d = lane; d < VD; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* src = part + ((size_t)s * total_rows + row) * LD;
+      acc = fmaf(src[d], ex2(src[VD] - top), acc);
+    }
+    out[(size_t)row * VD + d] = acc * inv;
+  }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -299,7 +351,9 @@ extern "C" int tllm_attention_maps_mma(const void* q, int q_row_stride, const vo
                                        float* out, int n_tokens, int n_requests, int max_q_len, int nq, int nkv, int maps,
                                        int kd, int vd, int page_size, long long k_page_stride, long long k_head_stride,
                                        long long v_page_stride, long long v_head_stride, float scale, int window, int chunk,
-                                       const float* sink, void* stream) {
+                                       const float* sink, int splits, float* part, void* stream) {
+  TLLM_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || (part != nullptr && max_q_len * (nq / nkv) <= BM)),
+               "attention_maps_mma: %d runs of key tiles need a buffer and rows that fit one tile", splits);
   TLLM_REQUIRE(kd == KD && vd == VD, "attention_maps_mma: built for key size %d and value size %d, called with %d and %d", KD, VD, kd, vd);
   TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && maps > 0,
                "attention_maps_mma: %d tokens, %d requests, %d heads, %d key/value heads, %d maps", n_tokens, n_requests, nq, nkv, maps);
@@ -315,6 +369,7 @@ extern "C" int tllm_attention_maps_mma(const void* q, int q_row_stride, const vo
   p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;
   p.q_row_stride = q_row_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.maps = maps; p.page_size = page_size;
   p.window = window; p.chunk = chunk; p.n_requests = n_requests;
+  p.splits = splits; p.part = part; p.total_rows = n_tokens * nq * maps;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.tiles_per_req = (int)(((long long)max_q_len * group + BM - 1) / BM);
   const long long gx = (long long)n_requests * p.tiles_per_req * nkv * maps;
@@ -327,6 +382,9 @@ extern "C" int tllm_attention_maps_mma(const void* q, int q_row_stride, const vo
     if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_maps_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  TLLM_LAUNCH("attention_maps_mma", attention_maps_kernel<ST>, dim3((unsigned)gx), 128, smem, (cudaStream_t)stream, p);
+  TLLM_LAUNCH("attention_maps_mma", attention_maps_kernel<ST>, dim3((unsigned)gx, (unsigned)splits), 128, smem, (cudaStream_t)stream, p);
+  if (splits > 1)
+    TLLM_LAUNCH("attention_maps_merge", attention_maps_merge_kernel, dim3((unsigned)((p.total_rows + 3) / 4)), 128, 0,
+                (cudaStream_t)stream, (const float*)part, out, sink, p.total_rows, splits, nq * maps, maps);
   return TLLM_OK;
 }

@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, attention_maps_splits, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -1230,12 +1230,15 @@ attention_maps_tc = os.environ.get("TLLM_ATTENTION_MAPS_TC", "1") != "0"
 # warps to every pair and so walks a pair's keys eight tiles at a time, instead of the tensor-core kernel, whose one
 # CTA per (request, key row) walks them tile after tile (0: always the tensor-core kernel; a switch for measurements).
 attention_maps_decode_pairs = int(os.environ.get("TLLM_ATTENTION_MAPS_DECODE_PAIRS", "0"))
+# Decoded tokens alone in a step: the tensor-core kernel cuts a row tile's key tiles into up to this many runs when its
+# grid (requests x key rows) would leave SMs idle; the runs' sums are joined by a second kernel (0 or 1: one run).
+attention_maps_splits = int(os.environ.get("TLLM_ATTENTION_MAPS_SPLITS", "16"))
 
 
 def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, maps: int, key_dim: int, value_dim: int,
                          k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, batch,
                          out: torch.Tensor, scale: float, window: Optional[int] = None,
-                         chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> None:
+                         chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None, workspace=None) -> None:
     """Attention with `maps` score maps per head over the same values, key rows of key_dim and value rows of
     value_dim values: query rows [head][map][key_dim] at the front of each `qkv` row, k_cache
     [pages, num_kv_heads * maps, page_size, key_dim], v_cache [pages, num_kv_heads, page_size, value_dim]; out
@@ -1245,7 +1248,8 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
     `batch`: token_request and positions per token
     (the CUDA-core kernel); cu_q, q_start per request, num_requests, max_q_len (the tensor-core kernel).
     bfloat16 with a float32 output and sizes that are multiples of 16 runs on the tensor cores, everything else on
-    the CUDA cores in 32-bit."""
+    the CUDA cores in 32-bit.  `workspace` (the step's named buffers): lets a step of decoded tokens cut the keys of a
+    row tile into runs that separate CTAs walk (needs batch.max_kv_len, an upper bound of the contexts)."""
     _need_cuda(qkv, k_cache, v_cache, block_table, out, sink)
     _i32(block_table, "block_table")
     t = qkv.shape[0]
@@ -1263,13 +1267,22 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
         lib = build.load_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
+        splits, part = 1, None
+        if workspace is not None and batch.max_q_len == 1 and attention_maps_splits > 1 and num_heads // num_kv_heads <= 64:
+            seen = batch.max_kv_len if not window else min(batch.max_kv_len, window + 64)
+            if chunk:
+                seen = min(seen, chunk)
+            ctas = batch.num_requests * num_kv_heads * maps
+            splits = max(1, min(attention_maps_splits, (4 * sm_count(qkv.device)) // ctas, (seen // 64 + 1) // 2))
+            if splits > 1:
+                part = workspace.get("attn_maps_part", (splits, t * num_heads * maps, value_dim + 2), torch.float32)
         _call(lib, lib.tllm_attention_maps_mma,
               _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
               _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
               num_kv_heads, maps, key_dim, value_dim, k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)),
               ctypes.c_longlong(k_cache.stride(1)), ctypes.c_longlong(v_cache.stride(0)),
               ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale), int(window or 0), int(chunk or 0), _ptr(sink),
-              _stream())
+              splits, _ptr(part), _stream())
         return
     lib = build.load_library("attention_generic")
     _call(lib, lib.tllm_paged_attention_maps,

@@ -104,7 +104,7 @@ class SinkAttention:
         # with a gate the attention leaves float32 rows and the gate kernel rounds them; without, it writes `out` itself
         attn = ctx.workspace.get("attn_maps", (t, self.o_dim), torch.float32) if self.gate else out
         ops.paged_attention_maps(proj, nh, nkv, 1, kd, vd, cache.k, cache.v, cache.block_table, ctx.batch, attn,
-                                 self.scale, self.window, None, sink=self.w_sink)
+                                 self.scale, self.window, None, sink=self.w_sink, workspace=ctx.workspace)
         if self.gate:
             off = self.q_dim + self.k_dim + self.v_dim
             ops.sigmoid_gate(attn, proj[:, off:off + self.o_dim], nh, vd, out)
@@ -176,7 +176,7 @@ class LatentAttention:
         ops.head_linear(proj[:, :nh * qd].view(t, nh, qd)[:, :, :nd], self.w_uk_t, q_lat[:, :, :rank])
         attn = ctx.workspace.get("attn_maps", (t, nh * rank), torch.float32)
         ops.paged_attention_maps(q_lat.view(t, nh * kd), nh, 1, 1, kd, rank, cache.k, cache.v, cache.block_table,
-                                 ctx.batch, attn, self.scale, self.window, None, sink=self.w_sink)
+                                 ctx.batch, attn, self.scale, self.window, None, sink=self.w_sink, workspace=ctx.workspace)
         gated = ctx.workspace.get("latent_o", (t, nh * rank), ctx.dtype)
         ops.sigmoid_gate(attn, proj[:, self.q_dim + kd:self.q_dim + kd + nh], nh, rank, gated)
         out = ctx.workspace.get("attn_out", (t, nh * vd), ctx.dtype)
