@@ -7,8 +7,9 @@
 // head_linear_mma (bfloat16, K even, rows and heads of `a` at even offsets): a CTA of four warps owns 64 tokens x 64
 //   outputs of one head; a warp 16 tokens x 64 outputs as eight m16n8k16 tiles.  The fragments are read straight from
 //   global memory: a thread's two neighbouring values of A or W are one 32-bit load (W's K runs contiguously, which is
-//   the column-major B the instruction takes), a head's weights stay in L1.  Sums are 32-bit, an output's sum runs
-//   over ascending k in steps of 16 whatever its tile, so its bits do not depend on the batch.
+//   the column-major B the instruction takes), a head's weights stay in L1.  Steps of at most 32 tokens give a CTA 16
+//   tokens and each of its warps 16 of the 64 outputs instead.  Sums are 32-bit, an output's sum runs over ascending
+//   k in steps of 16 whatever its tile, so its bits do not depend on the batch.
 // head_linear_simt (both dtypes, every size): tiles of 16 tokens x 64 outputs x 32 k through shared memory, four
 //   tokens of one output per thread, every output one chain of fmaf over ascending k.
 #include <cstdint>
@@ -36,27 +37,31 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TO>
+// FEW = false: the CTA's four warps take 16 token rows each and all 64 outputs.  FEW = true (steps of few tokens): the
+// CTA has 16 token rows and its warps 16 outputs each, so that a decode step's weights are fetched by four warps.
+template <typename TO, bool FEW>
 __global__ void __launch_bounds__(128) head_linear_mma_kernel(HeadLinearArgs p) {
+  constexpr int NT = FEW ? 2 : 8;     // tiles of 8 outputs per warp
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tg = lane & 3;
   const int h = blockIdx.z;
-  const int row0 = blockIdx.y * 64 + warp * 16;
-  const int n0 = blockIdx.x * 64;
-  if (row0 >= p.tokens) return;
+  const int row0 = FEW ? blockIdx.y * 16 : blockIdx.y * 64 + warp * 16;
+  const int n0 = blockIdx.x * 64 + (FEW ? warp * 16 : 0);
+  if (row0 >= p.tokens || n0 >= p.n) return;
   const __nv_bfloat16* a = (const __nv_bfloat16*)p.a + (size_t)h * p.a_hs;
   const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (size_t)h * p.n * p.k;
   const int r_lo = row0 + g, r_hi = row0 + g + 8;
   const bool lo_ok = r_lo < p.tokens, hi_ok = r_hi < p.tokens;
   const __nv_bfloat16* a_lo = a + (size_t)r_lo * p.a_ld;
   const __nv_bfloat16* a_hi = a + (size_t)r_hi * p.a_ld;
-  float acc[8][4];
+  float acc[NT][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+  for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+#pragma unroll 4
   for (int k0 = 0; k0 < p.k; k0 += 16) {
     const int ka = k0 + 2 * tg, kb = ka + 8;     // K is even: a pair is inside or outside as a whole
     uint32_t fa[4];
@@ -65,7 +70,7 @@ __global__ void __launch_bounds__(128) head_linear_mma_kernel(HeadLinearArgs p) 
     fa[2] = (lo_ok && kb < p.k) ? *(const uint32_t*)(a_lo + kb) : 0u;
     fa[3] = (hi_ok && kb < p.k) ? *(const uint32_t*)(a_hi + kb) : 0u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < NT; ++j) {
       const int n = n0 + j * 8 + g;
       const __nv_bfloat16* wr = w + (size_t)n * p.k;
       const uint32_t b0 = (n < p.n && ka < p.k) ? *(const uint32_t*)(wr + ka) : 0u;
@@ -75,7 +80,7 @@ __global__ void __launch_bounds__(128) head_linear_mma_kernel(HeadLinearArgs p) 
   }
   TO* out = (TO*)p.out + (size_t)h * p.o_hs;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NT; ++j) {
     const int n = n0 + j * 8 + 2 * tg;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -145,11 +150,14 @@ extern "C" int tllm_head_linear(const void* a, long long a_ld, int a_hs, const v
   const bool mma = tensor_cores && dtype == TLLM_BF16 && k % 2 == 0 && a_ld % 2 == 0 && a_hs % 2 == 0 &&
                    ((uintptr_t)a % 4) == 0 && ((uintptr_t)w % 4) == 0;
   if (mma) {
-    const long long gy = ((long long)tokens + 63) / 64;
+    const bool few = tokens <= 32;
+    const long long gy = few ? ((long long)tokens + 15) / 16 : ((long long)tokens + 63) / 64;
     TLLM_REQUIRE(gy <= 65535, "head_linear: %d tokens exceed the grid", tokens);
     const dim3 grid((n + 63) / 64, (unsigned)gy, heads);
-    if (out_dtype == TLLM_F32) TLLM_LAUNCH("head_linear_mma", head_linear_mma_kernel<float>, grid, 128, 0, s, p);
-    else TLLM_LAUNCH("head_linear_mma", head_linear_mma_kernel<__nv_bfloat16>, grid, 128, 0, s, p);
+    if (few && out_dtype == TLLM_F32) TLLM_LAUNCH("head_linear_mma", (head_linear_mma_kernel<float, true>), grid, 128, 0, s, p);
+    else if (few) TLLM_LAUNCH("head_linear_mma", (head_linear_mma_kernel<__nv_bfloat16, true>), grid, 128, 0, s, p);
+    else if (out_dtype == TLLM_F32) TLLM_LAUNCH("head_linear_mma", (head_linear_mma_kernel<float, false>), grid, 128, 0, s, p);
+    else TLLM_LAUNCH("head_linear_mma", (head_linear_mma_kernel<__nv_bfloat16, false>), grid, 128, 0, s, p);
     return TLLM_OK;
   }
   const long long gy = ((long long)tokens + 15) / 16;
