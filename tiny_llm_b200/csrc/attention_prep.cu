@@ -5,8 +5,10 @@
 // qk_norm_kv_write: rows of the projection are [nq query heads | nkv key heads] of kd values, then nkv value heads of
 //   vd values.  Optional biases are added; query and key heads are divided by sqrt(mean(x^2) + eps) and multiplied by
 //   a weight of kd values shared by the heads (no weights: no norm); the query is further multiplied by
-//   1 + coef * ln(floor((p + 1) / every) + 1) at position p (every = 0: not).  Queries are rewritten in place, keys
-//   and values go to their pages.  One warp per head row.
+//   1 + coef * ln(floor((p + 1) / every) + 1) at position p (every = 0: not).  With a frequency table the first
+//   rot_dims values of every query and key head are then turned by p * freq[i], value i with i + rot_dims / 2 or value
+//   2i with 2i + 1, cos and sin times a constant.  Queries are rewritten in place, keys and values go to their pages.
+//   One warp per head row.
 // latent_kv_write: rows are [nq query heads of (nd plain | rd rotated) values | rank latent values | rd rotated key
 //   values | ...].  The latent is normed (weight of rank values) and written both as the first `rank` values of the
 //   token's key row and as its value row; the key's rotated part and every query head's rotated part are turned in
@@ -35,10 +37,14 @@ struct QkArgs {
   int page_size;
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
   int n_tokens;
+  const float* freq;            // [rot_dims / 2] or null: query and key heads are rotated behind the norm
+  int rot_dims, rot_pairs;      // the first rot_dims values of a head turn; pairs (2i, 2i + 1) or halves (i, i + rot_dims / 2)
+  float rot_mag;                // cos and sin are multiplied by this
 };
 
 template <typename T>
 __global__ void __launch_bounds__(128) qk_norm_kv_write_kernel(QkArgs a) {
+  __shared__ float turned[4][MAX_ROW];
   pdl_trigger();
   pdl_wait();
   const int rows = a.nq + 2 * a.nkv;
@@ -77,14 +83,33 @@ __global__ void __launch_bounds__(128) qk_norm_kv_write_kernel(QkArgs a) {
   float stretch = 1.f;
   if (is_q && a.every > 0) stretch = fmaf(a.coef, logf((float)((a.positions[t] + 1) / a.every + 1)), 1.f);
   T* dst = is_q ? src : (T*)a.kcache + page * a.k_page_stride + (long long)h * a.k_head_stride + off * a.kd;
+  float* mine = turned[threadIdx.x >> 5];
 #pragma unroll
   for (int i = 0; i < MAX_ROW / 32; ++i) {
     const int d = lane + 32 * i;
     if (d < a.kd) {
       float y = w ? __fmul_rn(__fmul_rn(x[i], f), w[d]) : x[i];
       if (is_q) y = __fmul_rn(y, stretch);
-      dst[d] = from_f32<T>(y);
+      if (a.rot_dims > 0) mine[d] = y;
+      else dst[d] = from_f32<T>(y);
     }
+  }
+  if (a.rot_dims == 0) return;
+  // the rotation reads the normed values in 32-bit (the partner of a value lies with another lane) and rounds once
+  __syncwarp();
+  const float pos = (float)a.positions[t];
+  const int half = a.rot_dims / 2;
+  for (int d = lane; d < a.kd; d += 32) {
+    float y = mine[d];
+    if (d < a.rot_dims) {
+      const int i = a.rot_pairs ? d >> 1 : (d < half ? d : d - half);
+      const bool first = a.rot_pairs ? !(d & 1) : d < half;
+      const float u = mine[a.rot_pairs ? 2 * i : i], v = mine[a.rot_pairs ? 2 * i + 1 : i + half];
+      const float ang = __fmul_rn(pos, a.freq[i]);
+      const float c = __fmul_rn(cosf(ang), a.rot_mag), sn = __fmul_rn(sinf(ang), a.rot_mag);
+      y = first ? fmaf(u, c, -__fmul_rn(v, sn)) : fmaf(v, c, __fmul_rn(u, sn));
+    }
+    dst[d] = from_f32<T>(y);
   }
 }
 
@@ -101,8 +126,11 @@ struct LatentArgs {
   int page_size;
   long long k_page_stride, v_page_stride;
   int n_tokens;
+  float rot_mag;             // cos and sin are multiplied by this
 };
 
+// With kcache == null the rows hold queries only: their rotated parts are turned and nothing is written to a cache
+// (a mixer that reads the latents and key parts another layer cached).
 // One CTA of 128 threads per token: warp 0 norms the latent, all threads turn the rotated parts.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatentArgs a) {
@@ -115,14 +143,15 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatentArgs a) {
   const float pos = (float)a.positions[t];
   for (int i = threadIdx.x; i < a.rot_dims / 2; i += blockDim.x) {
     const float ang = __fmul_rn(pos, a.freq[i]);
-    cs[i] = cosf(ang);
-    sn[i] = sinf(ang);
+    cs[i] = __fmul_rn(cosf(ang), a.rot_mag);
+    sn[i] = __fmul_rn(sinf(ang), a.rot_mag);
   }
   __syncthreads();
   const T* row = (const T*)a.proj + (size_t)t * a.ld;
   const int qd = a.nd + a.rd, kd = a.rank + a.rd;
   const T* lat = row + (size_t)a.nq * qd;
-  const int slot = a.slot_mapping[t];
+  const bool writes = a.kcache != nullptr;
+  const int slot = writes ? a.slot_mapping[t] : -1;
   const long long page = slot / a.page_size, off = slot % a.page_size;
   T* krow = (T*)a.kcache + page * a.k_page_stride + off * kd;
   T* vrow = (T*)a.vcache + page * a.v_page_stride + off * a.rank;
@@ -190,7 +219,8 @@ extern "C" int tllm_qk_norm_kv_write(void* proj, int ld, int nq, int nkv, int kd
                                      const float* bv, const float* wq, const float* wk, float eps, float coef, int every,
                                      const int* positions, void* kcache, void* vcache, const int* slot_mapping,
                                      int page_size, long long k_page_stride, long long k_head_stride,
-                                     long long v_page_stride, long long v_head_stride, int n_tokens, int dtype, void* stream) {
+                                     long long v_page_stride, long long v_head_stride, int n_tokens, const float* freq,
+                                     int rot_dims, int rot_pairs, float rot_mag, int dtype, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && kd > 0 && kd <= MAX_ROW && vd > 0,
                "qk_norm_kv_write: %d tokens, %d / %d heads, key size %d (at most %d), value size %d", n_tokens, nq, nkv, kd, MAX_ROW, vd);
   TLLM_REQUIRE((wq == nullptr) == (wk == nullptr) && every >= 0 && page_size > 0 && kcache && vcache && slot_mapping && positions,
@@ -200,6 +230,9 @@ extern "C" int tllm_qk_norm_kv_write(void* proj, int ld, int nq, int nkv, int kd
   a.eps = eps; a.coef = coef; a.every = every; a.positions = positions; a.kcache = kcache; a.vcache = vcache;
   a.slot_mapping = slot_mapping; a.page_size = page_size; a.k_page_stride = k_page_stride; a.k_head_stride = k_head_stride;
   a.v_page_stride = v_page_stride; a.v_head_stride = v_head_stride; a.n_tokens = n_tokens;
+  TLLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= kd && (rot_dims == 0 || freq),
+               "qk_norm_kv_write: %d rotated values of %d (even, at most the head's size, with a frequency table)", rot_dims, kd);
+  a.freq = freq; a.rot_dims = rot_dims; a.rot_pairs = rot_pairs; a.rot_mag = rot_mag;
   const long long tasks = (long long)n_tokens * (nq + 2 * nkv), blocks = (tasks + 3) / 4;
   TLLM_REQUIRE(blocks <= 2147483647LL, "qk_norm_kv_write: %lld rows exceed the grid", tasks);
   cudaStream_t s = (cudaStream_t)stream;
@@ -212,17 +245,18 @@ extern "C" int tllm_qk_norm_kv_write(void* proj, int ld, int nq, int nkv, int kd
 extern "C" int tllm_latent_kv_write(const void* proj, int ld, int nq, int nd, int rd, int rank, int rot_dims,
                                     const float* w_latent, const float* freq, float eps, const int* positions, void* q_out,
                                     void* kcache, void* vcache, const int* slot_mapping, int page_size,
-                                    long long k_page_stride, long long v_page_stride, int n_tokens, int dtype, void* stream) {
+                                    long long k_page_stride, long long v_page_stride, int n_tokens, float rot_mag,
+                                    int dtype, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nd >= 0 && rd >= 0 && rank > 0 && rank <= MAX_ROW,
                "latent_kv_write: %d tokens, %d heads, sizes %d + %d, latent %d (at most %d)", n_tokens, nq, nd, rd, rank, MAX_ROW);
   TLLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rd && rot_dims <= 512 && (rot_dims == 0 || freq),
                "latent_kv_write: %d rotated values of %d (even, at most the part's size and 512, with a frequency table)", rot_dims, rd);
-  TLLM_REQUIRE(w_latent && positions && q_out && kcache && vcache && slot_mapping && page_size > 0, "latent_kv_write: a pointer is missing");
+  TLLM_REQUIRE(positions && q_out && page_size > 0 && (kcache == nullptr || (w_latent && vcache && slot_mapping)), "latent_kv_write: a pointer is missing");
   LatentArgs a;
   a.proj = proj; a.ld = ld; a.nq = nq; a.nd = nd; a.rd = rd; a.rank = rank; a.rot_dims = rot_dims; a.w_latent = w_latent;
   a.freq = freq; a.eps = eps; a.positions = positions; a.q_out = q_out; a.kcache = kcache; a.vcache = vcache;
   a.slot_mapping = slot_mapping; a.page_size = page_size; a.k_page_stride = k_page_stride; a.v_page_stride = v_page_stride;
-  a.n_tokens = n_tokens;
+  a.n_tokens = n_tokens; a.rot_mag = rot_mag;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32) TLLM_LAUNCH("latent_kv_write", latent_kv_write_kernel<float>, n_tokens, 128, 0, s, a);
   else if (dtype == TLLM_BF16) TLLM_LAUNCH("latent_kv_write", latent_kv_write_kernel<__nv_bfloat16>, n_tokens, 128, 0, s, a);

@@ -5,6 +5,13 @@
 // taps - 1 inputs of every channel are part of the request's state, beside S.  Decays, step sizes, unit norms, the
 // recurrence and the state are 32-bit; the projections are of the engine's dtype.
 //
+// Three variants share the kernels (`mode`):
+//   0  the rule above with one decay per head and token;
+//   1  a state-space recurrence without the correction, S <- g S + k (dt v)^T, o = S^T q, where the step size dt =
+//      softplus(b + dt_bias) also sets the decay g = exp(-exp(A_log) dt), the convolutions have a bias, nothing is made
+//      a unit vector, and the projection's channels come in the order [values | keys | queries];
+//   2  the rule above with a decay per head, key channel and token, S <- diag(g) S, from a 32-bit input row of its own.
+//
 // delta_prepare: one warp per (token, head row).  The channels of the fused projection's row are
 //   [kvh heads of queries | kvh heads of keys | heads of values | ...]; a row's channels are filtered over the
 //   request's earlier tokens in this step and, ahead of them, the inputs kept in the state; SiLU; query and key rows
@@ -44,6 +51,12 @@ struct PrepArgs {
   float q_scale, unit_eps;
   float *q, *k, *v, *gb;       // [T, kv_heads * kd] x 2, [T, heads * vd], [T, heads, 2] = (decay, step size)
   int n_tokens;
+  int q_c0, k_c0, v_c0;        // first channel of the queries, the keys and the values
+  const float* conv_bias;      // [channels] or null
+  int unit_norm;               // query and key heads are made unit vectors
+  int mode;                    // see the top of the file
+  const float* a_in;           // mode 2: [T, heads * kd] inputs of the decays (dt_bias has heads * kd values then)
+  float* gk;                   // mode 2: [T, heads * kd] decays
 };
 
 template <typename T>
@@ -64,18 +77,19 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(PrepArgs a) {
   float* dst;
   const bool is_v = u >= 2 * a.kv_heads;
   if (!is_v) {
-    c0 = u * a.kd; size = a.kd;
-    dst = (u < a.kv_heads ? a.q + (size_t)t * a.kv_heads * a.kd + (size_t)u * a.kd
-                          : a.k + (size_t)t * a.kv_heads * a.kd + (size_t)(u - a.kv_heads) * a.kd);
+    const bool is_q = u < a.kv_heads;
+    const int hh = is_q ? u : u - a.kv_heads;
+    c0 = (is_q ? a.q_c0 : a.k_c0) + hh * a.kd; size = a.kd;
+    dst = (is_q ? a.q : a.k) + (size_t)t * a.kv_heads * a.kd + (size_t)hh * a.kd;
   } else {
     const int h = u - 2 * a.kv_heads;
-    c0 = 2 * a.kv_heads * a.kd + h * a.vd; size = a.vd;
+    c0 = a.v_c0 + h * a.vd; size = a.vd;
     dst = a.v + (size_t)t * a.heads * a.vd + (size_t)h * a.vd;
   }
   float ss = 0.f;
   for (int d = lane; d < size; d += 32) {
     const int c = c0 + d;
-    float y = 0.f;
+    float y = a.conv_bias ? a.conv_bias[c] : 0.f;
     for (int j = 0; j < a.n_taps; ++j) {
       const int n = t - first - (a.n_taps - 1) + j;   // index among the request's tokens of this step; < 0: kept ones
       const float x = n >= 0 ? to_f32(proj[(size_t)(first + n) * a.ld + c])
@@ -87,16 +101,32 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(PrepArgs a) {
     ss = fmaf(y, y, ss);
   }
   if (!is_v) {
-    ss = warp_sum(ss);
-    const float f = (u < a.kv_heads ? a.q_scale : 1.f) / sqrtf(ss + a.unit_eps);
-    __syncwarp();
-    for (int d = lane; d < size; d += 32) dst[d] = __fmul_rn(dst[d], f);
-  } else if (lane == 0) {
-    const int h = u - 2 * a.kv_heads;
-    const float za = to_f32(proj[(size_t)t * a.ld + a.a_col + h]) + a.dt_bias[h];
+    if (a.unit_norm) {
+      ss = warp_sum(ss);
+      const float f = (u < a.kv_heads ? a.q_scale : 1.f) / sqrtf(ss + a.unit_eps);
+      __syncwarp();
+      for (int d = lane; d < size; d += 32) dst[d] = __fmul_rn(dst[d], f);
+    }
+    return;
+  }
+  const int h = u - 2 * a.kv_heads;
+  if (a.mode == 2) {
+    const float rate = expf(a.a_log[h]);
+    const size_t at = ((size_t)t * a.heads + h) * a.kd;
+    for (int d = lane; d < a.kd; d += 32)
+      a.gk[at + d] = expf(-rate * softplus_f(a.a_in[at + d] + a.dt_bias[h * a.kd + d]));
+  }
+  if (lane == 0) {
     const float zb = to_f32(proj[(size_t)t * a.ld + a.beta_col + h]);
-    a.gb[((size_t)t * a.heads + h) * 2] = expf(-expf(a.a_log[h]) * softplus_f(za));
-    a.gb[((size_t)t * a.heads + h) * 2 + 1] = 1.f / (1.f + expf(-zb));
+    float* gb = a.gb + ((size_t)t * a.heads + h) * 2;
+    if (a.mode == 1) {
+      const float dt = softplus_f(zb + a.dt_bias[h]);
+      gb[0] = expf(-expf(a.a_log[h]) * dt);
+      gb[1] = dt;
+    } else {
+      gb[0] = a.mode == 2 ? 1.f : expf(-expf(a.a_log[h]) * softplus_f(to_f32(proj[(size_t)t * a.ld + a.a_col + h]) + a.dt_bias[h]));
+      gb[1] = 1.f / (1.f + expf(-zb));
+    }
   }
 }
 
@@ -130,6 +160,7 @@ struct ScanArgs {
   const int* cu_q;
   float* out;                    // [T, heads * vd]
   int heads, kv_heads, kd, vd;
+  const float* gk;               // mode 2: [T, heads * kd] decays per key channel
 };
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
@@ -143,7 +174,7 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int R>   // state rows per lane, a multiple of 4: R * DR_LANES >= key size
+template <int R, int MODE>   // R: state rows per lane, a multiple of 4: R * DR_LANES >= key size; MODE: see the top of the file
 __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   // A lane owns R consecutive state rows of its column (rows sub * R ... sub * R + R - 1), so that its part of a key
   // or query is read from shared memory in 16-byte pieces; a lane's part lies R + 4 floats from the next lane's, which
@@ -154,6 +185,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   // decay and step size
   __shared__ __align__(16) float sq[2][DR_TOK][KP], sk[2][DR_TOK][KP];
   __shared__ float sv[2][DR_TOK][DR_COLS], sg[2][DR_TOK][2];
+  __shared__ __align__(16) float sd[MODE == 2 ? 2 : 1][MODE == 2 ? DR_TOK : 1][MODE == 2 ? KP : 4];   // decays per key channel
   pdl_trigger();
   const int tid = threadIdx.x;
   const int sub = tid & (DR_LANES - 1), cl = tid / DR_LANES;
@@ -163,6 +195,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   const int kh = h / (a.heads / a.kv_heads);
   for (int i = tid; i < 2 * DR_TOK * KP; i += 128) { (&sq[0][0][0])[i] = 0.f; (&sk[0][0][0])[i] = 0.f; }
   for (int i = tid; i < 2 * DR_TOK * DR_COLS; i += 128) (&sv[0][0][0])[i] = 0.f;
+  if (MODE == 2) for (int i = tid; i < 2 * DR_TOK * KP; i += 128) (&sd[0][0][0])[i] = 0.f;
   pdl_wait();
   const int t0 = a.cu_q[req], t1 = a.cu_q[req + 1];
   float* st = a.state + (((size_t)a.slots[req] * a.heads + h) * a.vd + (col_ok ? col : 0)) * a.kd;
@@ -175,7 +208,8 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   __syncthreads();   // the zeros are in place before any copy lands beside them
   const int qk_ld = a.kv_heads * a.kd, v_ld = a.heads * a.vd;
   // 16-byte copies when a key row is made of whole pieces that start on 16-byte boundaries
-  const bool wide = (a.kd & 3) == 0 && ((((size_t)a.q) | ((size_t)a.k)) & 15) == 0;
+  const bool wide = (a.kd & 3) == 0 && ((((size_t)a.q) | ((size_t)a.k) | ((size_t)a.gk)) & 15) == 0;
+  const int g_ld = a.heads * a.kd;
   auto stage = [&](int buf, int tb) {
     const int nt = min(DR_TOK, t1 - tb);
     if (wide) {
@@ -186,6 +220,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
         const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
         cp_async16(&sq[buf][tt][at], a.q + src);
         cp_async16(&sk[buf][tt][at], a.k + src);
+        if (MODE == 2) cp_async16(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
       }
     } else {
       for (int i = tid; i < nt * a.kd; i += 128) {
@@ -194,6 +229,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
         const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
         cp_async4(&sq[buf][tt][at], a.q + src);
         cp_async4(&sk[buf][tt][at], a.k + src);
+        if (MODE == 2) cp_async4(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
       }
     }
     for (int i = tid; i < nt * DR_COLS; i += 128) {
@@ -229,11 +265,19 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
 #pragma unroll
       for (int i = 0; i < R; ++i) { kr[i] = kn[i]; qr[i] = qn[i]; }
       if (more) fetch(buf, tt + 1, kn, qn);   // the next token's parts are on their way during this token's sums
+      if (MODE == 2) {   // the rows decay first, each by its own factor; the sums below then see the decayed state
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 dv = *reinterpret_cast<const float4*>(&sd[buf][tt][sub * CH + i]);
+          s[i] = __fmul_rn(s[i], dv.x); s[i + 1] = __fmul_rn(s[i + 1], dv.y);
+          s[i + 2] = __fmul_rn(s[i + 2], dv.z); s[i + 3] = __fmul_rn(s[i + 3], dv.w);
+        }
+      }
       // four partial sums each, rows i, i + 4, i + 8, ... in one of them: short chains of dependent operations
       float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f}, pc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        pa[i & 3] = fmaf(s[i], kr[i], pa[i & 3]);
+        if (MODE != 1) pa[i & 3] = fmaf(s[i], kr[i], pa[i & 3]);
         pb[i & 3] = fmaf(s[i], qr[i], pb[i & 3]);
         pc[i & 3] = fmaf(kr[i], qr[i], pc[i & 3]);
       }
@@ -246,8 +290,8 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
         xb += __shfl_xor_sync(0xffffffffu, xb, o);
         xc += __shfl_xor_sync(0xffffffffu, xc, o);
       }
-      const float g = sg[buf][tt][0], beta = sg[buf][tt][1];
-      const float u = __fmul_rn(beta, fmaf(-g, xa, sv[buf][tt][cl]));
+      const float g = sg[buf][tt][0], beta = sg[buf][tt][1];   // mode 2: g = 1, the rows have decayed already
+      const float u = MODE == 1 ? __fmul_rn(beta, sv[buf][tt][cl]) : __fmul_rn(beta, fmaf(-g, xa, sv[buf][tt][cl]));
       const float o = fmaf(u, xc, __fmul_rn(g, xb));
 #pragma unroll
       for (int i = 0; i < R; ++i) s[i] = fmaf(kr[i], u, __fmul_rn(g, s[i]));
@@ -271,15 +315,66 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   }
 }
 
+
+// gated_group_norm: y = (o + D_h x) * silu(z), then y / sqrt(mean(y^2) + eps) * w over each of `parts` equal parts of a
+// token's row (a part need not be a head), in 32-bit; one CTA per (token, part).  o, x float32 [T, width] (x and D
+// may be absent), z rows of ldz values in the engine's dtype, w float32 [width], out [T, width] in the engine's dtype.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __restrict__ o, const float* __restrict__ x,
+                                                               const float* __restrict__ skip, const T* __restrict__ z,
+                                                               int ldz, const float* __restrict__ w, T* __restrict__ out,
+                                                               int width, int parts, int vd, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const long long t = blockIdx.x / parts;
+  const int part = blockIdx.x % parts, size = width / parts, c0 = part * size;
+  const float* orow = o + t * width;
+  const float* xrow = x ? x + t * width : nullptr;
+  const T* zrow = z + t * ldz;
+  auto value = [&](int c) {
+    float y = orow[c];
+    if (xrow) y = fmaf(skip[c / vd], xrow[c], y);
+    const float g = to_f32(zrow[c]);
+    return __fmul_rn(y, g / (1.f + expf(-g)));
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) {
+    const float y = value(c0 + i);
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float r = 1.f / sqrtf(ss / (float)size + eps);
+  for (int i = threadIdx.x; i < size; i += blockDim.x)
+    out[t * width + c0 + i] = from_f32<T>(__fmul_rn(__fmul_rn(value(c0 + i), r), w[c0 + i]));
+}
+
 }  // namespace tllm
 
 using namespace tllm;
+
+extern "C" int tllm_gated_group_norm(const float* o, const float* x, const float* skip, const void* z, int ldz,
+                                     const float* w, void* out, long long n_tokens, int width, int parts, int vd,
+                                     float eps, int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && width > 0 && parts > 0 && width % parts == 0 && vd > 0 && (x == nullptr) == (skip == nullptr),
+               "gated_group_norm: %lld tokens, width %d in %d parts, heads of %d", n_tokens, width, parts, vd);
+  const long long blocks = n_tokens * parts;
+  TLLM_REQUIRE(blocks <= 2147483647LL, "gated_group_norm: %lld parts exceed the grid", blocks);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    TLLM_LAUNCH("gated_group_norm", gated_group_norm_kernel<float>, (unsigned)blocks, 128, 0, s, o, x, skip, (const float*)z, ldz, w, (float*)out, width, parts, vd, eps);
+  else if (dtype == TLLM_BF16)
+    TLLM_LAUNCH("gated_group_norm", gated_group_norm_kernel<__nv_bfloat16>, (unsigned)blocks, 128, 0, s, o, x, skip, (const __nv_bfloat16*)z, ldz, w, (__nv_bfloat16*)out, width, parts, vd, eps);
+  else TLLM_FAIL(TLLM_ERR_ARG, "gated_group_norm: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
 
 extern "C" int tllm_delta_prepare(const void* proj, int ld, const float* taps, int n_taps, const float* kept,
                                   const int* slots, const int* cu_q, const int* token_request, int heads, int kv_heads,
                                   int kd, int vd, int beta_col, int a_col, const float* a_log, const float* dt_bias,
                                   float q_scale, float unit_eps, float* q, float* k, float* v, float* gb, int n_tokens,
-                                  int dtype, void* stream) {
+                                  int q_c0, int k_c0, int v_c0, const float* conv_bias, int unit_norm, int mode,
+                                  const float* a_in, float* gk, int dtype, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && kd > 0 && vd > 0 && n_taps >= 1,
                "delta_prepare: %d tokens, %d heads over %d query/key heads, sizes %d / %d, %d taps", n_tokens, heads, kv_heads, kd, vd, n_taps);
   PrepArgs a;
@@ -287,6 +382,8 @@ extern "C" int tllm_delta_prepare(const void* proj, int ld, const float* taps, i
   a.token_request = token_request; a.heads = heads; a.kv_heads = kv_heads; a.kd = kd; a.vd = vd; a.beta_col = beta_col;
   a.a_col = a_col; a.a_log = a_log; a.dt_bias = dt_bias; a.q_scale = q_scale; a.unit_eps = unit_eps; a.q = q; a.k = k;
   a.v = v; a.gb = gb; a.n_tokens = n_tokens;
+  TLLM_REQUIRE(mode >= 0 && mode <= 2 && (mode != 2 || (a_in && gk)), "delta_prepare: mode %d (0, 1 or 2; 2 needs the decays' inputs and outputs)", mode);
+  a.q_c0 = q_c0; a.k_c0 = k_c0; a.v_c0 = v_c0; a.conv_bias = conv_bias; a.unit_norm = unit_norm; a.mode = mode; a.a_in = a_in; a.gk = gk;
   const long long tasks = (long long)n_tokens * (2 * kv_heads + heads);
   const long long blocks = (tasks + 3) / 4;
   TLLM_REQUIRE(blocks <= 2147483647LL, "delta_prepare: %lld rows exceed the grid", tasks);
@@ -314,18 +411,30 @@ extern "C" int tllm_conv_state_update(const void* proj, int ld, float* kept, con
 
 extern "C" int tllm_delta_rule_scan(const float* q, const float* k, const float* v, const float* gb, float* state,
                                     const int* slots, const int* cu_q, float* out, int heads, int kv_heads, int kd, int vd,
-                                    int n_requests, void* stream) {
+                                    int n_requests, int mode, const float* gk, void* stream) {
   TLLM_REQUIRE(n_requests > 0 && n_requests <= 65535 && heads > 0 && heads <= 65535 && kv_heads > 0 && heads % kv_heads == 0,
                "delta_rule_scan: %d requests, %d heads over %d query/key heads", n_requests, heads, kv_heads);
   TLLM_REQUIRE(kd >= 1 && kd <= 256 && vd >= 1, "delta_rule_scan: key size %d (at most 256), value size %d", kd, vd);
   ScanArgs a;
   a.q = q; a.k = k; a.v = v; a.gb = gb; a.state = state; a.slots = slots; a.cu_q = cu_q; a.out = out; a.heads = heads;
-  a.kv_heads = kv_heads; a.kd = kd; a.vd = vd;
+  a.kv_heads = kv_heads; a.kd = kd; a.vd = vd; a.gk = gk;
+  TLLM_REQUIRE(mode >= 0 && mode <= 2 && (mode == 2) == (gk != nullptr), "delta_rule_scan: mode %d (0, 1 or 2; decays per key channel with 2 only)", mode);
   const dim3 grid((vd + DR_COLS - 1) / DR_COLS, heads, n_requests);
   cudaStream_t s = (cudaStream_t)stream;
-  if (kd <= 32) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<4>, grid, 128, 0, s, a);
-  else if (kd <= 64) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<8>, grid, 128, 0, s, a);
-  else if (kd <= 128) TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<16>, grid, 128, 0, s, a);
-  else TLLM_LAUNCH("delta_rule_scan", delta_rule_scan_kernel<32>, grid, 128, 0, s, a);
+#define TLLM_SCAN(R)                                                                                         \
+  do {                                                                                                       \
+    if (mode == 0) TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<R, 0>), grid, 128, 0, s, a);       \
+    else if (mode == 1) TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<R, 1>), grid, 128, 0, s, a);  \
+    else TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<R, 2>), grid, 128, 0, s, a);                 \
+  } while (0)
+  if (kd <= 32) TLLM_SCAN(4);
+  else if (kd <= 64) TLLM_SCAN(8);
+  else if (kd <= 128) TLLM_SCAN(16);
+  else {   // three staged arrays of 256 rows would not fit a CTA's static shared memory
+    TLLM_REQUIRE(mode != 2, "delta_rule_scan: key size %d (at most 128 with a decay per key channel)", kd);
+    if (mode == 0) TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<32, 0>), grid, 128, 0, s, a);
+    else TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<32, 1>), grid, 128, 0, s, a);
+  }
+#undef TLLM_SCAN
   return TLLM_OK;
 }

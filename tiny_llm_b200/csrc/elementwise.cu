@@ -690,3 +690,104 @@ extern "C" int tllm_rope_kv_write(void* qkv, float* src, int src_stride, const i
     TLLM_FAIL(TLLM_ERR_ARG, "rope_kv_write: unknown dtype code %d", dtype);
   return TLLM_OK;
 }
+
+// ---------------------------------------------------------------- hashed bigram rows added into the stream
+// out[t, :] += table[row_t, :] with row_t = (prev_t * mul_prev + tokens[t] * mul_cur) mod buckets, prev_t the token
+// before t in its sequence; a sequence's first token takes row `buckets`.  The token before a step's first one is
+// the request's state (`last` [slots] int32), which the CTA of the request's first token of the step reads and then
+// replaces by the request's last token of the step: one launch, one reader and one writer per slot.
+namespace tllm {
+template <typename T>
+__global__ void bigram_add_kernel(const int* __restrict__ tokens, const int* __restrict__ token_request,
+                                  const int* __restrict__ cu_q, const int* __restrict__ q_start,
+                                  const int* __restrict__ slots, int* __restrict__ last, const T* __restrict__ table,
+                                  float* __restrict__ out, int n_tokens, int hidden, long long buckets,
+                                  long long mul_prev, long long mul_cur) {
+  __shared__ long long s_row;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  if (threadIdx.x == 0) {
+    const int req = token_request[t];
+    const int first = cu_q[req];
+    long long row = buckets;
+    if (t > first) {
+      row = ((long long)tokens[t - 1] * mul_prev + (long long)tokens[t] * mul_cur) % buckets;
+    } else {
+      int* slot = last + slots[req];
+      if (q_start[req] > 0) row = ((long long)*slot * mul_prev + (long long)tokens[t] * mul_cur) % buckets;
+      *slot = tokens[cu_q[req + 1] - 1];
+    }
+    s_row = row;
+  }
+  __syncthreads();
+  const T* src = table + (size_t)s_row * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] += to_f32(src[i]);
+}
+
+// ---------------------------------------------------------------- element by element: a copy in another type, or relu(x)^2
+template <typename TI, typename TO>
+__global__ void unary_kernel(const TI* __restrict__ x, TO* __restrict__ out, long long n, int act) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = to_f32(x[i]);
+    if (act == 1) { v = fmaxf(v, 0.f); v = __fmul_rn(v, v); }
+    out[i] = from_f32<TO>(v);
+  }
+}
+
+// resid += scale * x, element by element in 32-bit; clear != 0 hands x back zeroed
+__global__ void scaled_add_kernel(float* __restrict__ x, float* __restrict__ resid, long long n, float scale, int clear) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    resid[i] = fmaf(scale, x[i], resid[i]);
+    if (clear) x[i] = 0.f;
+  }
+}
+}  // namespace tllm
+
+extern "C" int tllm_bigram_add(const int* tokens, const int* token_request, const int* cu_q, const int* q_start,
+                               const int* slots, int* last, const void* table, float* out, int n_tokens, int hidden,
+                               long long buckets, long long mul_prev, long long mul_cur, int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && hidden > 0 && buckets > 0, "bigram_add: %d tokens, width %d, %lld buckets", n_tokens, hidden, buckets);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    TLLM_LAUNCH("bigram_add", bigram_add_kernel<float>, n_tokens, threads, 0, s, tokens, token_request, cu_q, q_start, slots, last, (const float*)table, out, n_tokens, hidden, buckets, mul_prev, mul_cur);
+  else if (dtype == TLLM_BF16)
+    TLLM_LAUNCH("bigram_add", bigram_add_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, tokens, token_request, cu_q, q_start, slots, last, (const __nv_bfloat16*)table, out, n_tokens, hidden, buckets, mul_prev, mul_cur);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "bigram_add: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
+
+// act: 0 = the value as it is (a copy in the output's type), 1 = relu(x)^2
+extern "C" int tllm_unary(const void* x, void* out, long long n, int in_dtype, int out_dtype, int act, void* stream) {
+  TLLM_REQUIRE(n > 0 && (act == 0 || act == 1), "unary: %lld values, activation code %d", n, act);
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (in_dtype == TLLM_F32 && out_dtype == TLLM_F32)
+    TLLM_LAUNCH("unary", (unary_kernel<float, float>), blocks, threads, 0, s, (const float*)x, (float*)out, n, act);
+  else if (in_dtype == TLLM_F32 && out_dtype == TLLM_BF16)
+    TLLM_LAUNCH("unary", (unary_kernel<float, __nv_bfloat16>), blocks, threads, 0, s, (const float*)x, (__nv_bfloat16*)out, n, act);
+  else if (in_dtype == TLLM_BF16 && out_dtype == TLLM_BF16)
+    TLLM_LAUNCH("unary", (unary_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, threads, 0, s, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, act);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "unary: dtype codes %d -> %d are not built", in_dtype, out_dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_scaled_add(float* x, float* resid, long long n, float scale, int clear, void* stream) {
+  TLLM_REQUIRE(n > 0, "scaled_add: empty input");
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  TLLM_LAUNCH("scaled_add", scaled_add_kernel, blocks, threads, 0, (cudaStream_t)stream, x, resid, n, scale, clear);
+  return TLLM_OK;
+}

@@ -16,7 +16,7 @@
 // kernel walks each request's summaries in order and leaves every segment's S_in in their place; a third walks the
 // segments again from there, now writing outputs.  The recurrence is linear in S, so the two ways differ by rounding only.
 //
-// head_norm_gate: y = o / sqrt(mean(o^2) + eps) * w * silu(g) per (token, head), 32-bit in, engine dtype out.
+// head_norm_gate: y = o / sqrt(mean(o^2) + eps) * w * silu(g) (or sigmoid(g)) per (token, head), 32-bit in, engine dtype out.
 #include "common.cuh"
 
 TLLM_DEFINE_LAST_ERROR
@@ -256,7 +256,7 @@ __global__ void linear_attention_prefix_kernel(ScanArgs a) {
 
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, const T* __restrict__ g,
-                                      int ldg, int heads, int vd, float eps, T* __restrict__ out, long long n_rows) {
+                                      int ldg, int heads, int vd, float eps, T* __restrict__ out, long long n_rows, int act) {
   pdl_trigger();
   pdl_wait();
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -273,7 +273,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   T* y = out + row * vd;
   for (int j = lane; j < vd; j += 32) {
     const float gv = to_f32(gr[j]);
-    const float sg = gv / (1.f + expf(-gv));
+    const float sg = (act == 1 ? 1.f : gv) / (1.f + expf(-gv));   // act 1: sigmoid, else silu
     float val = x[j] * r;
     if (w) val *= w[j];
     y[j] = from_f32<T>(val * sg);
@@ -341,16 +341,16 @@ extern "C" int tllm_linear_attention_scan(const void* q, const void* k, const vo
 
 // o: float32 [n_rows = T * heads, vd]; w: float32 [vd] or null; g: [T, heads * vd] rows of ldg values; out: [T, heads * vd].
 extern "C" int tllm_head_norm_gate(const float* o, const float* w, const void* g, int ldg, int heads, int vd, float eps,
-                                   void* out, long long n_rows, int dtype, void* stream) {
+                                   void* out, long long n_rows, int dtype, int act, void* stream) {
   TLLM_REQUIRE(n_rows > 0 && heads > 0 && vd > 0, "head_norm_gate: empty input");
   const int warps = 4;
   const long long blocks = (n_rows + warps - 1) / warps;
   TLLM_REQUIRE(blocks <= 2147483647LL, "head_norm_gate: %lld rows exceed the grid", n_rows);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)
-    TLLM_LAUNCH("head_norm_gate", head_norm_gate_kernel<float>, (unsigned)blocks, warps * 32, 0, s, o, w, (const float*)g, ldg, heads, vd, eps, (float*)out, n_rows);
+    TLLM_LAUNCH("head_norm_gate", head_norm_gate_kernel<float>, (unsigned)blocks, warps * 32, 0, s, o, w, (const float*)g, ldg, heads, vd, eps, (float*)out, n_rows, act);
   else if (dtype == TLLM_BF16)
-    TLLM_LAUNCH("head_norm_gate", head_norm_gate_kernel<__nv_bfloat16>, (unsigned)blocks, warps * 32, 0, s, o, w, (const __nv_bfloat16*)g, ldg, heads, vd, eps, (__nv_bfloat16*)out, n_rows);
+    TLLM_LAUNCH("head_norm_gate", head_norm_gate_kernel<__nv_bfloat16>, (unsigned)blocks, warps * 32, 0, s, o, w, (const __nv_bfloat16*)g, ldg, heads, vd, eps, (__nv_bfloat16*)out, n_rows, act);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "head_norm_gate: unknown dtype code %d", dtype);
   return TLLM_OK;

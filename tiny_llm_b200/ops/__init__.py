@@ -371,8 +371,8 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, hea
 
 
 def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: torch.Tensor, heads: int, value_dim: int,
-                   eps: float, out: torch.Tensor) -> None:
-    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per (token, head); o float32
+                   eps: float, out: torch.Tensor, act: str = "silu") -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]) per (token, head), act = silu or sigmoid; o float32
     [T, heads * value_dim], weight float32 [value_dim] or None, gate and out [T, heads * value_dim] in the engine's dtype."""
     _need_cuda(o, weight, gate, out)
     t = o.shape[0]
@@ -380,9 +380,12 @@ def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: torch.
             gate.stride(1) != 1 or out.shape != o.shape or not out.is_contiguous() or out.dtype != gate.dtype or \
             (weight is not None and (weight.dtype != torch.float32 or weight.numel() != value_dim)):
         raise KernelError("head_norm_gate: shapes or dtypes do not fit")
+    if act not in ("silu", "sigmoid"):
+        raise KernelError(f"head_norm_gate: unknown gate activation {act!r} (known: silu, sigmoid)")
     lib = build.load_library("linear_attention")
     _call(lib, lib.tllm_head_norm_gate, _ptr(o), _ptr(weight), _ptr(gate), gate.stride(0), heads, value_dim,
-          ctypes.c_float(eps), _ptr(out), ctypes.c_longlong(t * heads), _code(out.dtype), _stream())
+          ctypes.c_float(eps), _ptr(out), ctypes.c_longlong(t * heads), _code(out.dtype), 1 if act == "sigmoid" else 0,
+          _stream())
 
 
 def _paged(name: str, c: torch.Tensor, rows: int, dim: int) -> None:
@@ -678,13 +681,18 @@ def qk_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int
                      bias_q: Optional[torch.Tensor] = None, bias_k: Optional[torch.Tensor] = None,
                      bias_v: Optional[torch.Tensor] = None, norm_q: Optional[torch.Tensor] = None,
                      norm_k: Optional[torch.Tensor] = None, eps: float = 0.0, stretch_coef: float = 0.0,
-                     stretch_every: int = 0) -> None:
+                     stretch_every: int = 0, freq: Optional[torch.Tensor] = None, rot_pairs: bool = False,
+                     rot_mag: float = 1.0) -> None:
     """Rows of `proj` begin with num_heads query heads and num_kv_heads key heads of key_dim values, then num_kv_heads
     value heads of value_dim values.  Biases (float32) are added; with norm weights (float32 [key_dim], shared by the
     heads) query and key heads become x / sqrt(mean(x^2) + eps) * weight; with stretch_every > 0 the query at position
-    p is multiplied by 1 + stretch_coef * ln(floor((p + 1) / stretch_every) + 1).  Queries are rewritten in place, keys
+    p is multiplied by 1 + stretch_coef * ln(floor((p + 1) / stretch_every) + 1).  With `freq` (float32, n values) the
+    first 2n values of every query and key head are then turned by positions[t] * freq[i] in 32-bit, value i with
+    i + n (rot_pairs: value 2i with 2i + 1), cos and sin multiplied by rot_mag.  Queries are rewritten in place, keys
     and values go to their pages."""
-    _need_cuda(proj, positions, k_cache, v_cache, slot_mapping, bias_q, bias_k, bias_v, norm_q, norm_k)
+    _need_cuda(proj, positions, k_cache, v_cache, slot_mapping, bias_q, bias_k, bias_v, norm_q, norm_k, freq)
+    if freq is not None and (freq.dtype != torch.float32 or not freq.is_contiguous() or 2 * freq.numel() > key_dim):
+        raise KernelError("qk_norm_kv_write: the frequencies are contiguous float32, at most half a head's size of them")
     _i32(positions, "positions")
     _i32(slot_mapping, "slot_mapping")
     t = proj.shape[0]
@@ -705,22 +713,37 @@ def qk_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int
           _ptr(bias_q), _ptr(bias_k), _ptr(bias_v), _ptr(norm_q), _ptr(norm_k), ctypes.c_float(eps),
           ctypes.c_float(stretch_coef), int(stretch_every), _ptr(positions), _ptr(k_cache), _ptr(v_cache),
           _ptr(slot_mapping), k_cache.shape[2], ll(k_cache.stride(0)), ll(k_cache.stride(1)), ll(v_cache.stride(0)),
-          ll(v_cache.stride(1)), t, _code(proj.dtype), _stream())
+          ll(v_cache.stride(1)), t, _ptr(freq), 0 if freq is None else 2 * freq.numel(), 1 if rot_pairs else 0,
+          ctypes.c_float(rot_mag), _code(proj.dtype), _stream())
 
 
 def latent_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int, plain_dim: int, rot_part: int,
-                    rank: int, rot_dims: int, freq: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
-                    q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+                    rank: int, rot_dims: int, freq: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
+                    q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                    slot_mapping: Optional[torch.Tensor], rot_mag: float = 1.0) -> None:
     """Rows of `proj`: num_heads query heads of [plain_dim | rot_part] values, then `rank` latent values and rot_part
     key values shared by the heads.  The latent, normed with `norm_weight`, becomes the first `rank` values of the
     token's key row and its whole value row; the key's part and every query head's part are rotated pairwise (value
     2i with 2i + 1, i < rot_dims / 2) by positions[t] * freq[i]; the key part is written behind the latent, the query
-    parts to q_out[t, head, rank:] (q_out [T, num_heads, rank + rot_part])."""
+    parts to q_out[t, head, rank:] (q_out [T, num_heads, rank + rot_part]).  cos and sin are multiplied by rot_mag.
+    Without caches (k_cache None) the rows hold the query heads only and only their parts are turned: the form of a
+    mixer that reads what another layer cached."""
     _need_cuda(proj, positions, freq, norm_weight, q_out, k_cache, v_cache, slot_mapping)
     _i32(positions, "positions")
     _i32(slot_mapping, "slot_mapping")
     t = proj.shape[0]
     kd = rank + rot_part
+    if k_cache is None:
+        if proj.stride(1) != 1 or proj.shape[1] < num_heads * (plain_dim + rot_part) or q_out.shape != (t, num_heads, kd) or \
+                not q_out.is_contiguous() or q_out.dtype != proj.dtype or \
+                (rot_dims and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rot_dims)):
+            raise KernelError("latent_kv_write: the rows of the projection or of the query buffer do not fit")
+        lib = build.load_library("attention_prep")
+        _call(lib, lib.tllm_latent_kv_write, _ptr(proj), proj.stride(0), num_heads, plain_dim, rot_part, rank, rot_dims,
+              _ptr(None), _ptr(freq if rot_dims else None), ctypes.c_float(eps), _ptr(positions), _ptr(q_out),
+              _ptr(None), _ptr(None), _ptr(None), 1, ctypes.c_longlong(0), ctypes.c_longlong(0), t,
+              ctypes.c_float(rot_mag), _code(proj.dtype), _stream())
+        return
     if proj.stride(1) != 1 or proj.shape[1] < num_heads * (plain_dim + rot_part) + kd or \
             q_out.shape != (t, num_heads, kd) or not q_out.is_contiguous() or q_out.dtype != proj.dtype:
         raise KernelError("latent_kv_write: the rows of the projection or of the query buffer do not fit")
@@ -735,7 +758,7 @@ def latent_kv_write(proj: torch.Tensor, positions: torch.Tensor, num_heads: int,
     _call(lib, lib.tllm_latent_kv_write, _ptr(proj), proj.stride(0), num_heads, plain_dim, rot_part, rank, rot_dims,
           _ptr(norm_weight), _ptr(freq if rot_dims else None), ctypes.c_float(eps), _ptr(positions), _ptr(q_out),
           _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), k_cache.shape[2], ll(k_cache.stride(0)), ll(v_cache.stride(0)),
-          t, _code(proj.dtype), _stream())
+          t, ctypes.c_float(rot_mag), _code(proj.dtype), _stream())
 
 
 def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -771,31 +794,50 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, value_dim: int
           ctypes.c_longlong(t), heads, value_dim, _code(out.dtype), _stream())
 
 
+PREPARE_MODES = {"delta": 0, "state_space": 1, "channel_decay": 2}
+
+
 def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, kept: torch.Tensor, batch, heads: int, kv_heads: int,
                   key_dim: int, value_dim: int, beta_col: int, a_col: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
-                  q_scale: float, unit_eps: float, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch.Tensor) -> None:
+                  q_scale: float, unit_eps: float, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch.Tensor,
+                  mode: str = "delta", conv_bias: Optional[torch.Tensor] = None, decay_in: Optional[torch.Tensor] = None,
+                  gk: Optional[torch.Tensor] = None) -> None:
     """The inputs of the delta rule from the fused projection.  The first kv_heads * key_dim * 2 + heads * value_dim
     columns of `proj` are the channels [queries | keys | values]; each is filtered over time with its row of `taps`
     (float32 [channels, n]; the last column meets the current token; ahead of the step's tokens stand the inputs in
     kept[slot] (float32 [slots, n - 1, channels], oldest first)), then SiLU.  Query and key heads are divided by
     sqrt(sum(x^2) + unit_eps), queries also multiplied by q_scale.  Columns beta_col + h and a_col + h hold the step
     size's and the decay's inputs: gb[t, h] = (exp(-exp(a_log[h]) softplus(a + dt_bias[h])), sigmoid(b)).  q, k, v, gb
-    are float32."""
-    _need_cuda(proj, taps, kept, a_log, dt_bias, q, k, v, gb)
+    are float32.
+    mode "channel_decay": the decay is one per head and key channel, gk[t, h, c] = exp(-exp(a_log[h]) softplus(decay_in[t, h, c]
+    + dt_bias[h, c])) from float32 rows `decay_in`, and gb[t, h] = (1, sigmoid(b)); a_col is not read.
+    mode "state_space": the channels are [values | keys | queries], the filters add `conv_bias` (float32 [channels]),
+    nothing is made a unit vector, and gb[t, h] = (exp(-exp(a_log[h]) dt), dt) with dt = softplus(b + dt_bias[h])."""
+    _need_cuda(proj, taps, kept, a_log, dt_bias, q, k, v, gb, conv_bias, decay_in, gk)
     t = proj.shape[0]
     channels = 2 * kv_heads * key_dim + heads * value_dim
     n = taps.shape[1]
+    if mode not in PREPARE_MODES:
+        raise KernelError(f"delta_prepare: unknown mode {mode!r} (known: {', '.join(PREPARE_MODES)})")
+    qk = kv_heads * key_dim
+    q_c0, k_c0, v_c0 = (heads * value_dim + qk, heads * value_dim, 0) if mode == "state_space" else (0, qk, 2 * qk)
+    n_bias = heads * key_dim if mode == "channel_decay" else heads
+    if (mode == "channel_decay") != (decay_in is not None and gk is not None) or \
+            (conv_bias is not None and (conv_bias.dtype != torch.float32 or conv_bias.numel() != channels or not conv_bias.is_contiguous())) or \
+            any(x is not None and (x.dtype != torch.float32 or not x.is_contiguous() or x.shape != (t, heads * key_dim)) for x in (decay_in, gk)):
+        raise KernelError("delta_prepare: the decays' rows or the filters' bias do not fit the mode")
     if proj.stride(1) != 1 or proj.shape[1] < max(channels, beta_col + heads, a_col + heads) or \
             taps.dtype != torch.float32 or taps.shape != (channels, n) or not taps.is_contiguous() or \
             kept.dtype != torch.float32 or not kept.is_contiguous() or tuple(kept.shape[1:]) != (max(n - 1, 1), channels) or \
             any(x.dtype != torch.float32 or not x.is_contiguous() for x in (a_log, dt_bias, q, k, v, gb)) or \
-            a_log.numel() != heads or dt_bias.numel() != heads or q.shape != (t, kv_heads * key_dim) or k.shape != q.shape or \
+            a_log.numel() != heads or dt_bias.numel() != n_bias or q.shape != (t, kv_heads * key_dim) or k.shape != q.shape or \
             v.shape != (t, heads * value_dim) or gb.shape != (t, heads, 2):
         raise KernelError("delta_prepare: shapes or dtypes do not fit")
     lib = build.load_library("delta_rule")
     _call(lib, lib.tllm_delta_prepare, _ptr(proj), proj.stride(0), _ptr(taps), n, _ptr(kept), _ptr(batch.slots),
           _ptr(batch.cu_q), _ptr(batch.token_request), heads, kv_heads, key_dim, value_dim, beta_col, a_col, _ptr(a_log),
           _ptr(dt_bias), ctypes.c_float(q_scale), ctypes.c_float(unit_eps), _ptr(q), _ptr(k), _ptr(v), _ptr(gb), t,
+          q_c0, k_c0, v_c0, _ptr(conv_bias), 0 if mode == "state_space" else 1, PREPARE_MODES[mode], _ptr(decay_in), _ptr(gk),
           _code(proj.dtype), _stream())
 
 
@@ -812,11 +854,16 @@ def conv_state_update(proj: torch.Tensor, kept: torch.Tensor, batch, n_taps: int
 
 
 def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch.Tensor, state: torch.Tensor, batch,
-                    heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor) -> None:
+                    heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor, mode: str = "delta",
+                    gk: Optional[torch.Tensor] = None) -> None:
     """Per head and token, in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q, with (g, beta) =
     gb[t, h]; head h reads query/key head h // (heads / kv_heads).  All float32; state [slots, heads, value_dim,
-    key_dim] (the transpose of S) is carried from step to step."""
-    _need_cuda(q, k, v, gb, state, out)
+    key_dim] (the transpose of S) is carried from step to step.  mode "channel_decay": S <- diag(gk[t, h]) S instead of
+    g S (gk float32 [T, heads * key_dim]).  mode "state_space": no correction, u = beta v."""
+    _need_cuda(q, k, v, gb, state, out, gk)
+    if mode not in PREPARE_MODES or (mode == "channel_decay") != (gk is not None) or \
+            (gk is not None and (gk.dtype != torch.float32 or not gk.is_contiguous() or gk.shape != (q.shape[0], heads * key_dim))):
+        raise KernelError(f"delta_rule_scan: mode {mode!r} and the decays per key channel do not fit")
     t = q.shape[0]
     if any(x.dtype != torch.float32 or not x.is_contiguous() for x in (q, k, v, gb, state, out)) or \
             q.shape != (t, kv_heads * key_dim) or k.shape != q.shape or v.shape != (t, heads * value_dim) or \
@@ -824,7 +871,102 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gb: torch
         raise KernelError("delta_rule_scan: shapes or dtypes do not fit")
     lib = build.load_library("delta_rule")
     _call(lib, lib.tllm_delta_rule_scan, _ptr(q), _ptr(k), _ptr(v), _ptr(gb), _ptr(state), _ptr(batch.slots),
-          _ptr(batch.cu_q), _ptr(out), heads, kv_heads, key_dim, value_dim, batch.num_requests, _stream())
+          _ptr(batch.cu_q), _ptr(out), heads, kv_heads, key_dim, value_dim, batch.num_requests, PREPARE_MODES[mode],
+          _ptr(gk), _stream())
+
+
+def bigram_add(tokens: torch.Tensor, table: torch.Tensor, last: torch.Tensor, batch, out: torch.Tensor, mul_prev: int,
+               mul_cur: int) -> None:
+    """out[t] += table[(prev_t * mul_prev + tokens[t] * mul_cur) mod buckets] with buckets = rows of `table` - 1 and
+    prev_t the token before t in its sequence; a sequence's first token takes the table's last row.  The token before
+    a step's first one is last[slot] (int32 [slots, 1]), which this launch also replaces by the step's last token."""
+    _need_cuda(tokens, table, last, out)
+    _i32(tokens, "tokens")
+    _i32(last, "last")
+    t, h = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous() or table.shape[1] != h or \
+            table.shape[0] < 2 or tokens.numel() != t or last.numel() != last.shape[0]:
+        raise KernelError("bigram_add: shapes or dtypes do not fit")
+    ll = ctypes.c_longlong
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_bigram_add, _ptr(tokens), _ptr(batch.token_request), _ptr(batch.cu_q), _ptr(batch.q_start),
+          _ptr(batch.slots), _ptr(last), _ptr(table), _ptr(out), t, h, ll(table.shape[0] - 1), ll(mul_prev), ll(mul_cur),
+          _code(table.dtype), _stream())
+
+
+UNARY_ACTS = {"copy": 0, "relu2": 1}
+
+
+def unary(x: torch.Tensor, out: torch.Tensor, act: str = "copy") -> None:
+    """out = act(x) element by element, computed in 32-bit and rounded once to out's dtype: "copy" (x in another
+    dtype) or "relu2" (relu(x)^2).  x float32 or of out's dtype."""
+    _need_cuda(x, out)
+    if x.shape != out.shape or not x.is_contiguous() or not out.is_contiguous() or act not in UNARY_ACTS or \
+            x.dtype not in (torch.float32, out.dtype):
+        raise KernelError("unary: shapes, dtypes or activation do not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_unary, _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _code(x.dtype), _code(out.dtype),
+          UNARY_ACTS[act], _stream())
+
+
+def scaled_add(x: torch.Tensor, scale: float, resid: torch.Tensor, clear: bool = True) -> None:
+    """resid += scale * x, all float32; clear=True hands `x` back zeroed (a branch buffer that products add into)."""
+    _need_cuda(x, resid)
+    if x.dtype != torch.float32 or resid.dtype != torch.float32 or x.shape != resid.shape or not x.is_contiguous() or \
+            not resid.is_contiguous():
+        raise KernelError("scaled_add: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_scaled_add, _ptr(x), _ptr(resid), ctypes.c_longlong(x.numel()), ctypes.c_float(scale),
+          1 if clear else 0, _stream())
+
+
+def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, parts: int, value_dim: int, eps: float,
+                     out: torch.Tensor, skip_x: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None) -> None:
+    """y = (o + skip[h] * skip_x) * silu(gate), then each of `parts` equal parts of a row is divided by its root mean
+    square (eps inside the root) and multiplied by `weight`; the gate comes before the norm.  o, skip_x float32
+    [T, width], skip float32 [width / value_dim] (one per head), gate (a row slice is fine) and out [T, width] in the
+    engine's dtype, weight float32 [width]."""
+    _need_cuda(o, gate, weight, out, skip_x, skip)
+    t, width = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or gate.shape != o.shape or gate.stride(1) != 1 or \
+            out.shape != o.shape or not out.is_contiguous() or out.dtype != gate.dtype or weight.dtype != torch.float32 or \
+            weight.numel() != width or width % parts or width % value_dim or (skip_x is None) != (skip is None) or \
+            (skip_x is not None and (skip_x.dtype != torch.float32 or skip_x.shape != o.shape or not skip_x.is_contiguous() or
+                                     skip.dtype != torch.float32 or skip.numel() != width // value_dim)):
+        raise KernelError("gated_group_norm: shapes or dtypes do not fit")
+    lib = build.load_library("delta_rule")
+    _call(lib, lib.tllm_gated_group_norm, _ptr(o), _ptr(skip_x), _ptr(skip), _ptr(gate), gate.stride(0), _ptr(weight),
+          _ptr(out), ctypes.c_longlong(t), width, parts, value_dim, ctypes.c_float(eps), _code(out.dtype), _stream())
+
+
+def attention_talk(q: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, block_table: torch.Tensor, batch, mix: torch.Tensor, out: torch.Tensor,
+                   window: Optional[int] = None, sink: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> None:
+    """Attention whose heads' scores are mixed before the softmax: z_h = sum_g mix[h, g] (q_g . k), softmax over the
+    visible keys (the last `window`, or all earlier ones), optionally with exp(sink[h]) in the denominator, head h's
+    output optionally times sigmoid(gate[t, h]).  q: rows that begin with the query heads; caches [pages,
+    num_kv_heads, page_size, key_dim | value_dim]; mix float32 [heads, heads] (the score scale folded in); out
+    [T, heads * value_dim] in the cache's dtype or float32.  Everything but the reads is 32-bit."""
+    _need_cuda(q, k_cache, v_cache, block_table, mix, out, sink, gate)
+    _i32(block_table, "block_table")
+    t = q.shape[0]
+    _paged("attention_talk", k_cache, num_kv_heads, key_dim)
+    _paged("attention_talk", v_cache, num_kv_heads, value_dim)
+    if q.stride(1) != 1 or q.shape[1] < num_heads * key_dim or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or \
+            k_cache.shape[2] != v_cache.shape[2] or mix.dtype != torch.float32 or mix.shape != (num_heads, num_heads) or \
+            not mix.is_contiguous() or out.shape != (t, num_heads * value_dim) or not out.is_contiguous() or \
+            out.dtype not in (q.dtype, torch.float32) or \
+            (sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_contiguous())) or \
+            (gate is not None and (gate.dtype != q.dtype or gate.shape != (t, num_heads) or gate.stride(1) != 1)):
+        raise KernelError("attention_talk: shapes or dtypes do not fit")
+    ll = ctypes.c_longlong
+    lib = build.load_library("attention_talk")
+    _call(lib, lib.tllm_attention_talk, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+          block_table.shape[1], _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(mix), _ptr(sink), _ptr(gate),
+          0 if gate is None else gate.stride(0), _ptr(out), 1 if out.dtype == torch.float32 else 0, batch.num_requests,
+          batch.max_q_len, num_heads, num_kv_heads, key_dim, value_dim, k_cache.shape[2], ll(k_cache.stride(0)),
+          ll(k_cache.stride(1)), ll(v_cache.stride(0)), ll(v_cache.stride(1)), int(window or 0), _code(q.dtype), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -1349,7 +1491,7 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
 
 
 ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "attention_prep", "recurrence",
-                 "linear_attention", "delta_rule", "head_linear", "window_attention", "moe", "sampling")
+                 "linear_attention", "delta_rule", "head_linear", "window_attention", "attention_talk", "moe", "sampling")
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use

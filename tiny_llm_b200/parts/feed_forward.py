@@ -75,4 +75,37 @@ class SwiGLU:
         ops.linear(act, self.w_down, resid, accumulate=True)
 
 
+class DenseMLP:
+    """Two matrices around an activation, no gate: m = Wd act(Wu y), act = relu(.)^2.  The first product leaves 32-bit
+    sums; the activation is taken on them and rounded once."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, names=("up", "down"), act: str = "relu2",
+                 out_scale: float = 1.0):
+        if act not in ops.UNARY_ACTS or act == "copy":
+            raise ValueError(f"unknown activation {act!r}; known: relu2")
+        self.hidden_size, self.intermediate_size, self.names, self.act = hidden_size, intermediate_size, tuple(names), act
+        self.out_scale = float(out_scale)
+        self.w_up = self.w_down = None
+
+    def weight_specs(self, prefix: str):
+        u, d = self.names
+        return [WeightSpec(prefix + u, (self.intermediate_size, self.hidden_size), COMPUTE),
+                WeightSpec(prefix + d, (self.hidden_size, self.intermediate_size), COMPUTE)]
+
+    def load(self, prefix: str, weights) -> None:
+        u, d = self.names
+        self.w_up = weights[prefix + u]
+        self.w_down = scaled_matrix(weights[prefix + d], self.out_scale)
+
+    def forward(self, ctx, h, resid) -> None:
+        t = h.shape[0]
+        sums = ctx.workspace.get("ffn_sums", (t, self.intermediate_size), torch.float32)
+        ops.linear(h, self.w_up, sums)
+        act = ctx.workspace.get("ffn_act", (t, self.intermediate_size), ctx.dtype)
+        ops.unary(sums, act, self.act)
+        ops.linear(act, self.w_down, resid, accumulate=True)
+
+
 register_part("ffn", "swiglu", SwiGLU)
+register_part("ffn", "dense_mlp", DenseMLP)

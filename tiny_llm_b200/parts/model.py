@@ -126,6 +126,63 @@ class SandwichBlock:
 register_block("sandwich_norm", SandwichBlock)
 
 
+class BranchNormBlock:
+    """A norm BEHIND each branch only: x += norm1(mixer(x)); x += norm2(ffn(x)).  The branches read the stream itself
+    (rounded to the engine's dtype where that is not float32; the float32 engine hands them the stream as it is); a
+    branch adds its output into a zeroed float32 buffer, whose norm one kernel adds into the stream, handing the
+    buffer back zeroed.  `norm1` and `norm2` of the layer's spec are these norms."""
+
+    def __init__(self, spec: LayerSpec, shares_cache: bool = False):
+        for role in ("norm1", "mixer"):
+            if getattr(spec, role) is None:
+                raise ValueError(f"layer {spec.prefix!r}: a branch_norm block needs a {role}")
+        if (spec.ffn is None) != (spec.norm2 is None):
+            raise ValueError(f"layer {spec.prefix!r}: a branch_norm block has a norm2 exactly when it has a feed-forward")
+        if spec.residual_scale != 1.0:
+            raise ValueError(f"layer {spec.prefix!r}: a normed branch has no use for a residual scale")
+        self.spec = spec
+        self.norm1 = build_part("norm", spec.norm1)
+        self.mixer = build_part("mixer", spec.mixer, **({"shares_cache": True} if shares_cache else {}))
+        self.norm2 = None if spec.ffn is None else build_part("norm", spec.norm2)
+        self.ffn = None if spec.ffn is None else build_part("ffn", spec.ffn)
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def _named(self):
+        p, s = self.spec.prefix, self.spec
+        named = [(self.norm1, p + s.norm1_name), (self.mixer, p + s.mixer_prefix)]
+        if self.ffn is not None:
+            named += [(self.norm2, p + s.norm2_name), (self.ffn, p + s.ffn_prefix)]
+        return named
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [w for part, name in self._named() for w in part.weight_specs(name)]
+
+    def load(self, weights) -> None:
+        for part, name in self._named():
+            part.load(name, weights)
+
+    @staticmethod
+    def _input(ctx, resid):
+        if ctx.dtype == torch.float32:
+            return resid
+        h = ctx.workspace.get("norm_out", tuple(resid.shape), ctx.dtype)
+        ops.unary(resid, h)
+        return h
+
+    def forward(self, ctx, resid, cache) -> None:
+        branch = ctx.workspace.get_zeroed("branch_out", tuple(resid.shape))
+        self.mixer.forward(ctx, self._input(ctx, resid), branch, cache)
+        self.norm1.add_into(ctx, branch, resid)
+        if self.ffn is not None:
+            self.ffn.forward(ctx, self._input(ctx, resid), branch)
+            self.norm2.add_into(ctx, branch, resid)
+
+
+register_block("branch_norm", BranchNormBlock)
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
@@ -148,6 +205,7 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm)
         self.after_embedding = None if spec.after_embedding is None else build_part("hook", spec.after_embedding)
         self.on_logits = None if spec.on_logits is None else build_part("hook", spec.on_logits)
+        self._hook_keeps = self.after_embedding is not None and hasattr(self.after_embedding, "cache_need")
         self.embed = None
         self.lm_head = None
         self.loaded = False
@@ -181,10 +239,14 @@ class DecoderModel:
         return out
 
     def cache_needs(self):
-        """One need per run-order entry; None for an entry that reads another entry's cache or needs none."""
+        """One need per run-order entry; None for an entry that reads another entry's cache or needs none.  A hook
+        after the embedding that keeps something per request adds one more entry at the end."""
         def need(block):
             return None if block.mixer is None else block.mixer.cache_need()
-        return [None if c.reads_cache_of is not None else need(self.blocks[c.layer]) for c in self.spec.order]
+        needs = [None if c.reads_cache_of is not None else need(self.blocks[c.layer]) for c in self.spec.order]
+        if self._hook_keeps:   # what the hook after the embedding keeps per request comes behind the layer calls' entries
+            needs.append(self.after_embedding.cache_need())
+        return needs
 
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
         s = self.spec
@@ -207,7 +269,9 @@ class DecoderModel:
         b = ctx.batch
         resid = ctx.workspace.get("resid", (b.num_tokens, s.hidden_size), torch.float32)
         ops.embedding(b.tokens, self.embed, resid, scale=s.embedding_scale)
-        if self.after_embedding is not None:
+        if self._hook_keeps:
+            self.after_embedding.forward(ctx, resid, ctx.cache_view(len(s.order)))
+        elif self.after_embedding is not None:
             self.after_embedding.forward(ctx, resid)
         for pos, call in enumerate(s.order):
             owner = pos if call.reads_cache_of is None else call.reads_cache_of

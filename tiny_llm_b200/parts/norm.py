@@ -11,21 +11,27 @@ from .registry import register_part
 class RMSNorm:
     graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
-    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight", one_plus: bool = False):
+    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight", one_plus: bool = False,
+                 scalar: bool = False):
         """`weight_suffix`: what the weight is called behind the part's name ("" when the name is the tensor's).
-        `one_plus`: the norm multiplies by 1 + the stored weight (added once, in 32-bit, when the weight is loaded)."""
+        `one_plus`: the norm multiplies by 1 + the stored weight (added once, in 32-bit, when the weight is loaded).
+        `scalar`: the stored weight is ONE number for all coordinates (a tensor without dimensions); it is spread over
+        the row when it is loaded."""
         self.size = size
+        self.scalar = scalar
         self.eps = float(eps)
         self.weight_suffix = weight_suffix
         self.one_plus = one_plus
         self.weight = None
 
     def weight_specs(self, prefix: str):
-        init = {"init": ("normal", 0.1)} if self.one_plus else {}
-        return [WeightSpec(prefix + self.weight_suffix, (self.size,), FLOAT32, **init)]
+        init = {"init": ("normal", 0.1)} if self.one_plus else ({"init": ("uniform", 0.5, 1.5)} if self.scalar else {})
+        return [WeightSpec(prefix + self.weight_suffix, () if self.scalar else (self.size,), FLOAT32, **init)]
 
     def load(self, prefix: str, weights) -> None:
         w = weights[prefix + self.weight_suffix]
+        if self.scalar:
+            w = w.reshape(1).expand(self.size).contiguous()
         self.weight = (w + 1.0).contiguous() if self.one_plus else w
 
     def add_into(self, ctx, branch, resid) -> None:
