@@ -234,14 +234,15 @@ def talking_window_attention(m, w, p, h, positions, eps, quant):
     v = quant(h @ w[p + "v"].T).view(t, kvh, vd)
     q = rms_unit(q, eps) * w[p + "q.norm"].to(h.dtype)
     k = rms_unit(k, eps) * w[p + "k.norm"].to(h.dtype)
-    freq, mag = rotation_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"), h.dtype)
-    q = quant(rotate(q, positions, freq, mag, m["rot"]["dims"], "halves"))
-    k = quant(rotate(k, positions, freq, mag, m["rot"]["dims"], "halves"))
+    if m.get("rot"):
+        freq, mag = rotation_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"), h.dtype)
+        q, k = (rotate(x, positions, freq, mag, m["rot"]["dims"], "halves") for x in (q, k))
+    q, k = quant(q), quant(k)
     per = heads // kvh
     scores = torch.einsum("ihd,jhd->hij", q, k.repeat_interleave(per, dim=1)) * m["scale"]
     scores = scores * w[p + "temp"].to(h.dtype)[:, None, None]
     scores = torch.einsum("hg,gij->hij", w[p + "talk"].to(h.dtype), scores)
-    o = masked_softmax_attention(scores, v.repeat_interleave(per, dim=1).transpose(0, 1), window=m["mask"]["size"])
+    o = masked_softmax_attention(scores, v.repeat_interleave(per, dim=1).transpose(0, 1), window=(m.get("mask") or {}).get("size"))
     gate = torch.sigmoid(quant(h @ w[p + "g"].T))
     return quant((o * gate[:, :, None]).reshape(t, heads * vd)) @ w[p + "o"].T
 

@@ -78,7 +78,10 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
   }
   const T* kc = (const T*)a.kcache;
   const T* vc = (const T*)a.vcache;
-  for (int j0 = lo; j0 <= hi; j0 += TK_KEYS) {
+  // Key tiles begin at multiples of TK_KEYS whatever the tile of queries: a query then meets its keys in the same
+  // tiles, lanes and order however its prompt was cut and whatever shares its CTA (a tile or a lane that it does not
+  // see changes no bit of its sums), so the 32-bit results do not depend on the cut.
+  for (int j0 = lo - lo % TK_KEYS; j0 <= hi; j0 += TK_KEYS) {
     const int nk = min(TK_KEYS, hi - j0 + 1);
     __syncthreads();   // the tile before is read to its end (and the queries are in place)
     for (int idx = tid; idx < G * TK_KEYS * kd; idx += nthreads) {
