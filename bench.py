@@ -16,7 +16,8 @@ roofline of every decode point, and the clocks seen while timing.
 Dunelix model at the TinyLlama layer sizes beside the Llama decoder at equal sizes, and its kernels alone beside their
 like kernels, each against its roofline (`--only decode` with it: the decode points alone).  `--design zozenex` does
 the same for a Zozenex model (retention and gated linear attention, window attention with pooled blocks, routed
-experts) beside the Dunelix model at equal width, layers and vocabulary, `--design fiponex` for a Fiponex model (gated
+experts) beside the Dunelix model at equal width, layers and vocabulary, `--design gevovik` for a Gevovik model beside
+the Fiponex model, `--design fiponex` for a Fiponex model (gated
 delta rule, latent attention, attention with a sink, dense and routed gated feed-forwards) beside the Zozenex model."""
 import argparse
 import json
@@ -434,7 +435,7 @@ def spec_weight_bytes(model, itemsize):
             continue
         n = 1
         for d in w.shape:
-            n *= d
+            n *= w.free_dim if d is None else d    # a rank that only the stored tensor fixes: what random weights use
         total += n * (itemsize if w.keep == COMPUTE else 4)
     return total
 
@@ -936,6 +937,164 @@ def fiponex_kernels(dtype, device, pk, tokens=2048):
     return out
 
 
+# `--design gevovik`: a Gevovik model (latent attention with a sink over all earlier tokens, every second one of them
+# reading the cache of the one before; a state-space mixer; a window attention with mixed scores beside a delta rule with
+# decays per key channel; norms behind the branches; relu-squared feed-forwards; hashed bigram rows) at the same width,
+# layers and vocabulary, beside the Fiponex model above (the closest design the engine has: latent attention, the
+# delta rule, normed branches).
+def gevovik_shape(layers=DESIGN_LAYERS, width=2048, vocab=32000, ff=5632, window=1024):
+    dense = {"kind": "dense", "ff": ff}
+    rot = {"dims": 64, "base": 10000.0}
+    latent = {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 128 ** -0.5, "rot": rot}
+    mamba = {"heads": 32, "vdim": 128, "state": 128, "groups": 4, "norm_groups": 4, "conv": 4}
+    par = {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window},
+                    "rot": {"dims": 128, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}, "left_scale": 0.6, "right_scale": 1.1}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append({"type": "latent_attention", "mixer": dict(latent), "mlp": dense})
+        elif i % 4 == 1:
+            out.append({"type": "mamba2", "mixer": mamba, "mlp": dense})
+        elif i % 4 == 2:
+            out.append({"type": "parallel", "mixer": par, "mlp": dense})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 3), "mlp": dense})
+    return {"architecture": "Gevovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
+            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": out}
+
+
+def gevovik_kernels(dtype, device, pk, tokens=2048):
+    """The design's kernels alone at the sizes of one layer of the --design shape and `tokens` tokens of one prompt, and
+    their like kernels of the Fiponex path: microseconds, achieved GB/s or TFLOP/s, share of the peak."""
+    import types
+    import torch
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.parts import stretched_frequencies
+    t, width, page, window = tokens, 2048, PAGE, 1024
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    rnd = lambda *shape: torch.randn(*shape, device=device).to(dtype)
+    out = {}
+    isz = 2 if dtype == torch.bfloat16 else 4
+
+    def mem(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+
+    def flop(name, us, flops):
+        out[name] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+
+    pages = -(-t // page)
+    table = i32([list(range(pages))])
+    slots, pos = i32(list(range(t))), i32(list(range(t)))
+    meta = types.SimpleNamespace(token_request=i32([0] * t), positions=pos, cu_q=i32([0, t]), q_start=i32([0]), slots=i32([1]),
+                                 num_requests=1, num_tokens=t, max_q_len=t, max_kv_len=t, num_leading_decodes=0)
+
+    # the left mixer: head norms + stretched rotation + cache write, the attention with mixed scores and a gate per head
+    h, kvh, kd, vd = 16, 4, 128, 128
+    qkv = rnd(t, (h + kvh) * kd + kvh * vd + h)
+    kc = torch.zeros(pages, kvh, page, kd, dtype=dtype, device=device)
+    vc = torch.zeros(pages, kvh, page, vd, dtype=dtype, device=device)
+    nq, nk = torch.ones(kd, device=device), torch.ones(kd, device=device)
+    freq, mag = stretched_frequencies(kd, 10000.0, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    freq = freq.to(device)
+    mem("qk_norm_kv_write (head norms, stretched rotation in halves)", time_kernel(lambda: ops.qk_norm_kv_write(
+        qkv, pos, h, kvh, kd, vd, kc, vc, slots, None, None, None, nq, nk, eps=1e-6, freq=freq, rot_mag=mag), flush),
+        t * isz * (h * kd * 2 + (kvh * kd + kvh * vd) * 2))
+    mem("qk_norm_kv_write (like: biases, head norms, stretch)", time_kernel(lambda: ops.qk_norm_kv_write(
+        qkv, pos, h, kvh, kd, vd, kc, vc, slots, None, None, None, nq, nk, eps=1e-6, stretch_coef=0.1, stretch_every=1024), flush),
+        t * isz * (h * kd * 2 + (kvh * kd + kvh * vd) * 2))
+    mix = (torch.eye(h, device=device) + 0.1 * torch.randn(h, h, device=device)) * kd ** -0.5
+    att = torch.empty(t, h * vd, dtype=dtype, device=device)
+    off = (h + kvh) * kd + kvh * vd
+    wpairs = sum(min(p + 1, window) for p in range(t))
+    flop("attention_talk (16 heads of 128, 4 key/value heads, window 1024, mixed scores, gate per head)", time_kernel(
+        lambda: ops.attention_talk(qkv, h, kvh, kd, vd, kc, vc, table, meta, mix, att, window=window, gate=qkv[:, off:off + h]),
+        flush, repeats=5), 2.0 * wpairs * h * (kd + vd + h))
+    att32 = torch.empty(t, h * vd, dtype=torch.float32, device=device)
+    sink = torch.zeros(h, device=device)
+    flop("attention with a sink, window 1024 (like; tensor cores, scores not mixed)", time_kernel(lambda: ops.paged_attention_maps(
+        qkv, h, kvh, 1, kd, vd, kc, vc, table, meta, att32, kd ** -0.5, window, None, sink=sink), flush, repeats=5),
+        2.0 * wpairs * h * (kd + vd))
+
+    # the right mixer: the delta rule with decays per key channel
+    h, kvh, kd, vd, taps = 16, 8, 128, 128, 4
+    ch = 2 * kvh * kd + h * vd
+    proj = rnd(t, ch + 16 + h + 16)
+    w_taps = torch.randn(ch, taps, device=device) * 0.5
+    kept = torch.zeros(4, taps - 1, ch, device=device)
+    q, k = torch.empty(t, kvh * kd, device=device), torch.empty(t, kvh * kd, device=device)
+    v, gb = torch.empty(t, h * vd, device=device), torch.empty(t, h, 2, device=device)
+    a_log, dt_h, dt_c = torch.zeros(h, device=device), torch.zeros(h, device=device), torch.zeros(h * kd, device=device)
+    a_in, gk = torch.randn(t, h * kd, device=device), torch.empty(t, h * kd, device=device)
+    mem("delta_prepare (decays per key channel)", time_kernel(lambda: ops.delta_prepare(
+        proj, w_taps, kept, meta, h, kvh, kd, vd, ch + 16, ch + 16 + h, a_log, dt_c, kd ** -0.5, 1e-6, q, k, v, gb,
+        mode="channel_decay", decay_in=a_in, gk=gk), flush), t * (ch * (isz + 4) + h * kd * 8))
+    mem("delta_prepare (like: one decay per head)", time_kernel(lambda: ops.delta_prepare(
+        proj, w_taps, kept, meta, h, kvh, kd, vd, ch + 16, ch + 16 + h, a_log, dt_h, kd ** -0.5, 1e-6, q, k, v, gb), flush),
+        t * ch * (isz + 4))
+    state = torch.zeros(4, h, vd, kd, device=device)
+    o = torch.empty(t, h * vd, device=device)
+    us = time_kernel(lambda: ops.delta_rule_scan(q, k, v, gb, state, meta, h, kvh, kd, vd, o, mode="channel_decay", gk=gk), flush)
+    out["delta_rule_scan, decays per key channel (16 heads, 128 x 128)"] = {"us": round(us, 2), "fp32_tflops": round(t * h * kd * vd * 9.0 / us / 1e6, 2)}
+    state.zero_()
+    us = time_kernel(lambda: ops.delta_rule_scan(q, k, v, gb, state, meta, h, kvh, kd, vd, o), flush)
+    out["delta_rule_scan, one decay per head (like; 16 heads, 128 x 128)"] = {"us": round(us, 2), "fp32_tflops": round(t * h * kd * vd * 8.0 / us / 1e6, 2)}
+    state.zero_()
+    g = rnd(t, h * vd)
+    y = torch.empty(t, h * vd, dtype=dtype, device=device)
+    wn = torch.ones(vd, device=device)
+    mem("head_norm_gate with sigmoid (shared with the like)", time_kernel(lambda: ops.head_norm_gate(o, wn, g, h, vd, 1e-6, y, act="sigmoid"), flush),
+        t * h * vd * (4 + 2 * isz))
+
+    # the state-space mixer: 32 heads of 128 values, state 128, 4 groups
+    h, groups, n, vd = 32, 4, 128, 128
+    inner, bc = h * vd, groups * n
+    ch = inner + 2 * bc
+    proj = rnd(t, inner + ch + h)
+    conv_in = proj[:, inner:]
+    w_taps, b_taps = torch.randn(ch, taps, device=device) * 0.5, torch.zeros(ch, device=device)
+    kept = torch.zeros(4, taps - 1, ch, device=device)
+    q, k = torch.empty(t, bc, device=device), torch.empty(t, bc, device=device)
+    v, gb = torch.empty(t, inner, device=device), torch.empty(t, h, 2, device=device)
+    a_log, dt_h = torch.zeros(h, device=device), torch.zeros(h, device=device)
+    mem("delta_prepare (state-space form: bias, step sizes)", time_kernel(lambda: ops.delta_prepare(
+        conv_in, w_taps, kept, meta, h, groups, n, vd, ch, ch, a_log, dt_h, 1.0, 0.0, q, k, v, gb, mode="state_space",
+        conv_bias=b_taps), flush), t * ch * (isz + 4))
+    state = torch.zeros(4, h, vd, n, device=device)
+    o = torch.empty(t, inner, device=device)
+    us = time_kernel(lambda: ops.delta_rule_scan(q, k, v, gb, state, meta, h, groups, n, vd, o, mode="state_space"), flush)
+    out["delta_rule_scan, state-space form (32 heads, state 128 x 128 values)"] = {"us": round(us, 2), "fp32_tflops": round(t * h * n * vd * 6.0 / us / 1e6, 2)}
+    y = torch.empty(t, inner, dtype=dtype, device=device)
+    wn = torch.ones(inner, device=device)
+    skip = torch.ones(h, device=device)
+    mem("gated_group_norm (skip, gate, 4 parts)", time_kernel(lambda: ops.gated_group_norm(
+        o, proj[:, :inner], wn, 4, vd, 1e-6, y, skip_x=v, skip=skip), flush), t * inner * (8 + 2 * isz))
+
+    # the stream: bigram rows, the copy a branch reads, the norm behind a branch, the weighted sum, relu squared
+    x = torch.randn(t, width, device=device)
+    resid = torch.zeros(t, width, device=device)
+    tab = rnd(65522, width)
+    toks = torch.randint(0, 32000, (t,), dtype=torch.int32, device=device)
+    last = torch.zeros(4, 1, dtype=torch.int32, device=device)
+    mem("bigram_add", time_kernel(lambda: ops.bigram_add(toks, tab, last, meta, resid, 31, 17), flush), t * width * (isz + 8))
+    emb = rnd(32000, width)
+    mem("embedding (like)", time_kernel(lambda: ops.embedding(toks, emb, resid, scale=2.0), flush), t * width * (isz + 4))
+    yy = torch.empty(t, width, dtype=dtype, device=device)
+    mem("unary copy (the stream in the engine's dtype)", time_kernel(lambda: ops.unary(x, yy), flush), t * width * (4 + isz))
+    w1 = torch.ones(width, device=device)
+    mem("rms_norm (like)", time_kernel(lambda: ops.rms_norm(x, w1, 1e-6, yy), flush), t * width * (4 + isz))
+    mem("rms_norm_add (the norm behind a branch; shared with the like)", time_kernel(lambda: ops.rms_norm_add(x, w1, 1e-6, 1.0, resid), flush), t * width * 16)
+    mem("scaled_add (a side-by-side branch into the sum)", time_kernel(lambda: ops.scaled_add(x, 0.6, resid), flush), t * width * 16)
+    ff = 5632
+    sums = torch.randn(t, ff, device=device)
+    act = torch.empty(t, ff, dtype=dtype, device=device)
+    mem("unary relu squared from 32-bit sums", time_kernel(lambda: ops.unary(sums, act, "relu2"), flush), t * ff * (4 + isz))
+    du = rnd(t, 2 * ff)
+    mem("silu_mul with relu (like)", time_kernel(lambda: ops.silu_mul(du, act, 128, act="relu"), flush), t * ff * 3 * isz)
+    return out
+
+
 def design_run(args, dtype, device, pk):
     import gc
     import torch
@@ -955,12 +1114,20 @@ def design_run(args, dtype, device, pk):
                         "of 128, 4 taps) + dense gated feed-forward of 5632; the same + 32 gated experts of 1408, 4 chosen; latent "
                         "attention (16 heads, 64 plain + 64 rotated, values of 128, latent 192, window 1024) + experts; attention "
                         "with a sink (16 heads, 4 key/value heads, keys and values of 128, gate per value) + dense; beside: the "
-                        "Zozenex model of --design zozenex at equal width, layers and vocabulary"}
+                        "Zozenex model of --design zozenex at equal width, layers and vocabulary",
+             "gevovik": "width 2048, vocabulary 32000, hashed bigram rows of 65521 buckets; layers in turn: latent attention with a "
+                        "sink over all earlier tokens (16 heads, 64 plain + 64 rotated, values of 128, latent 192); state-space "
+                        "mixer (32 heads of 128, state 128, 4 groups, 4 taps); window attention with mixed scores (16 heads, 4 "
+                        "key/value heads, keys and values of 128, window 1024, stretched rotation, gate per head) beside a delta "
+                        "rule with decays per key channel (16 heads, 8 query/key heads, keys and values of 128, 4 taps); latent "
+                        "attention reading the first one's cache; every layer with a relu-squared feed-forward of 5632; beside: "
+                        "the Fiponex model of --design fiponex at equal width, layers and vocabulary"}
     result = {"design": args.design, "dtype": args.dtype, "layers": DESIGN_LAYERS, "peaks": pk["source"],
               "sizes": sizes[args.design],
               "l2": "whole steps: weights larger than L2; kernels alone: L2 flushed before every timed call"}
     sampler = ClockSampler().start()
-    labels = {"dunelix": ("dunelix", "llama"), "zozenex": ("zozenex", "dunelix"), "fiponex": ("fiponex", "zozenex")}[args.design]
+    labels = {"dunelix": ("dunelix", "llama"), "zozenex": ("zozenex", "dunelix"), "fiponex": ("fiponex", "zozenex"),
+              "gevovik": ("gevovik", "fiponex")}[args.design]
     for label in labels[:1 if args.only == "decode" else 2]:
         if label == "dunelix":
             cfg, model = build_design(dunelix_shape(), dtype, device)
@@ -968,6 +1135,8 @@ def design_run(args, dtype, device, pk):
             cfg, model = build_design(zozenex_shape(), dtype, device)
         elif label == "fiponex":
             cfg, model = build_design(fiponex_shape(), dtype, device)
+        elif label == "gevovik":
+            cfg, model = build_design(gevovik_shape(), dtype, device)
         else:
             cfg, model = build_model(DESIGN_LAYERS, dtype, device)
         runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
@@ -980,7 +1149,7 @@ def design_run(args, dtype, device, pk):
             ms, launched, ctx = timed_decode(runner, bsz, CONTEXT - (REPEATS * steps + warmup), steps, warmup, out, repeats=REPEATS)
             moved = design_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "dunelix" else \
                 zozenex_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "zozenex" else \
-                fiponex_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "fiponex" else \
+                fiponex_decode_bytes(model, runner, bsz, ctx, itemsize) if label in ("fiponex", "gevovik") else \
                 decode_bytes(model, runner, bsz, ctx, itemsize)
             rec[f"decode_b{bsz}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(bsz * 1e3 / ms, 1),
                                      "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "gpu_launches": launched}
@@ -990,7 +1159,8 @@ def design_run(args, dtype, device, pk):
         torch.cuda.empty_cache()
     result["clocks"] = sampler.stop()
     if dtype == torch.bfloat16 and args.only == "all":
-        result["kernels"] = {"dunelix": design_kernels, "zozenex": zozenex_kernels, "fiponex": fiponex_kernels}[args.design](dtype, device, pk)
+        result["kernels"] = {"dunelix": design_kernels, "zozenex": zozenex_kernels, "fiponex": fiponex_kernels,
+                             "gevovik": gevovik_kernels}[args.design](dtype, device, pk)
     ops.check_status()
     print(json.dumps(result))
     return 0
@@ -1015,7 +1185,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
-    ap.add_argument("--design", default=None, choices=["dunelix", "zozenex", "fiponex"],
+    ap.add_argument("--design", default=None, choices=["dunelix", "zozenex", "fiponex", "gevovik"],
                     help="instead of the flagship run: this design's prefill and decode at real layer sizes beside the Llama "
                          "decoder at equal sizes, and its kernels beside their like kernels (one plain line, no record)")
     ap.add_argument("--quick", action="store_true",

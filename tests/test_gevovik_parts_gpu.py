@@ -175,13 +175,18 @@ def paged(rows, page, n_pages, order, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 32, 20, 16), (6, 3, 10, 6, 3, 4), (8, 1, 40, 24, 129, 32), (2, 2, 12, 12, None, 8),
-                                   (5, 5, 8, 72, 64, 8), (16, 4, 20, 130, 33, 16), (24, 8, 8, 16, 17, 4)])
+                                   (5, 5, 8, 72, 64, 8), (16, 4, 20, 130, 33, 16), (24, 8, 8, 16, 17, 4),
+                                   # sizes the tensor-core kernel takes in bfloat16
+                                   (8, 2, 32, 16, 150, 32), (16, 4, 64, 48, 33, 16), (3, 1, 16, 16, None, 8), (12, 12, 128, 128, 100, 4)])
 def test_mixed_scores_attention_with_planted_keys(dtype, sizes):
     """One sequence of 300 tokens, attended as a whole prompt, in portions, and with its last tokens decoded alone
     beside another request.  Planted: for chosen queries one key far back, at a page border, at the window's first
     position and right outside it gets a score that stands out in ONE head, which the mixing spreads to the others."""
+    import math
     from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import Workspace
     heads, kvh, kd, vd, window, page = sizes
+    ws = Workspace(torch.device(DEV))
     g = torch.Generator().manual_seed(heads * 100 + kd)
     t = 300
     q = torch.randn(t, heads, kd, generator=g) * 0.5
@@ -230,7 +235,8 @@ def test_mixed_scores_attention_with_planted_keys(dtype, sizes):
             out = torch.empty(n, heads * vd, dtype=torch.float32 if use_sink else dtype, device=DEV)
             ops.attention_talk(qd, heads, kvh, kd, vd, kc, vc, bt.to(DEV), b, mix.to(DEV), out, window=window,
                                sink=sink.to(DEV) if use_sink else None,
-                               gate=gate_rows.to(dtype).to(DEV) if gate_rows is not None else None)
+                               gate=gate_rows.to(dtype).to(DEV) if gate_rows is not None else None,
+                               mix_log2=(mix.double() * math.log2(math.e)).float().to(DEV), workspace=ws)
             return out.view(n, heads, vd)
 
         def gates(rows):

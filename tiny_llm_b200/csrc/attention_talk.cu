@@ -6,7 +6,7 @@
 // A key is visible to a query at position p when it lies at p or before and, with a window, less than `window` back.
 // The mixing makes every head's weights depend on all heads' scores, so one CTA takes ALL heads of a tile of QT
 // consecutive queries of one request: warp g computes head g's scores against a staged tile of 32 keys (a lane per
-// key), the scores meet in shared memory, warp h mixes its row of them, keeps the running maximum and denominator of
+// key; fewer keys where 32 of all key/value heads do not fit the shared memory), the scores meet in shared memory, warp h mixes its row of them, keeps the running maximum and denominator of
 // its QT queries and adds the tile's weighted values (a lane per value column).  Scores, mixing, softmax and sums are
 // 32-bit on the CUDA cores for both dtypes; keys and values are read from their pages in the cache's dtype.
 #include "common.cuh"
@@ -15,7 +15,7 @@ TLLM_DEFINE_LAST_ERROR
 
 namespace tllm {
 
-constexpr int TK_KEYS = 32;   // keys per staged tile
+constexpr int TK_MAX = 32;   // keys per staged tile: a lane per key; 16, 8 or 4 where larger tiles of all key/value heads do not fit
 
 struct TalkArgs {
   const void* q;               // rows of ldq values; the first heads * kd are the query heads
@@ -33,6 +33,7 @@ struct TalkArgs {
   int heads, kv_heads, kd, vd, page_size;
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
   int window;                  // 0: every earlier key
+  int tk;                      // keys per staged tile
 };
 
 __host__ __device__ inline size_t talk_align(size_t x) { return (x + 15) & ~(size_t)15; }
@@ -42,7 +43,7 @@ template <typename T, int QT, int VC>
 __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kernel(TalkArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_trigger();
-  const int H = a.heads, G = a.kv_heads, kd = a.kd, vd = a.vd;
+  const int H = a.heads, G = a.kv_heads, kd = a.kd, vd = a.vd, TK_KEYS = a.tk;
   const int ks = kd + 1;   // a key row's stride in shared memory: a lane per key reads without bank conflicts
   size_t at = 0;
   float* sq = reinterpret_cast<float*>(smem + at); at = talk_align(at + sizeof(float) * QT * H * kd);
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
       float s[QT];
 #pragma unroll
       for (int i = 0; i < QT; ++i) s[i] = 0.f;
-      const float* kr = sk + (kvh * TK_KEYS + lane) * ks;
+      const float* kr = sk + (kvh * TK_KEYS + min(lane, TK_KEYS - 1)) * ks;
       const float* qr = sq + h * kd;
       if ((kd & 3) == 0) {
         for (int d = 0; d < kd; d += 4) {
@@ -126,7 +127,8 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
         }
       }
 #pragma unroll
-      for (int i = 0; i < QT; ++i) ss[(h * QT + i) * TK_KEYS + lane] = s[i];
+      for (int i = 0; i < QT; ++i)
+        if (lane < TK_KEYS) ss[(h * QT + i) * TK_KEYS + lane] = s[i];
     }
     __syncthreads();
     // head h's mixed scores, running maximum and denominator, and the tile's weights
@@ -134,7 +136,8 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
 #pragma unroll
     for (int i = 0; i < QT; ++i) {
       float z = 0.f;
-      for (int g = 0; g < H; ++g) z = fmaf(smix[h * H + g], ss[(g * QT + i) * TK_KEYS + lane], z);
+      if (lane < TK_KEYS)
+        for (int g = 0; g < H; ++g) z = fmaf(smix[h * H + g], ss[(g * QT + i) * TK_KEYS + lane], z);
       const int qpos = p0 + i;
       const bool seen = i < nq && lane < nk && kpos <= qpos && (a.window <= 0 || qpos - kpos < a.window);
       z = seen ? z : -INFINITY;
@@ -145,7 +148,7 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
       m[i] = m_new;
 #pragma unroll
       for (int c = 0; c < VC; ++c) acc[i][c] *= alpha;
-      sp[(h * TK_KEYS + lane) * QT + i] = p;
+      if (lane < TK_KEYS) sp[(h * TK_KEYS + lane) * QT + i] = p;
     }
     __syncwarp();
     const T* vr = sv + (size_t)kvh * TK_KEYS * vd;
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(QT * VC > 16 ? 512 : 1024) attention_talk_kern
   }
 }
 
-inline size_t talk_smem(int qt, int heads, int kv_heads, int kd, int vd, size_t elem) {
+inline size_t talk_smem(int qt, int TK_KEYS, int heads, int kv_heads, int kd, int vd, size_t elem) {
   size_t at = 0;
   at = talk_align(at + sizeof(float) * qt * heads * kd);
   at = talk_align(at + sizeof(float) * kv_heads * TK_KEYS * (kd + 1));
@@ -224,18 +227,23 @@ int talk_pick_vc(const TalkArgs& a, int n_requests, int max_q_len, size_t smem, 
 }
 
 template <typename T>
-int talk_pick(const TalkArgs& a, int n_requests, int max_q_len, cudaStream_t s) {
+int talk_pick(TalkArgs a, int n_requests, int max_q_len, cudaStream_t s) {
   constexpr size_t LIMIT = 200 * 1024;
   // as many queries per CTA as the shared memory holds (a key tile is staged once for all of them); one for decoding
+  // The keys per tile depend on the model's sizes alone (never on the step), so that a query meets its keys in the
+  // same tiles whatever the step looks like.
+  int tk = TK_MAX;
+  while (tk > 4 && talk_smem(1, tk, a.heads, a.kv_heads, a.kd, a.vd, sizeof(T)) > LIMIT) tk >>= 1;
   int qt = max_q_len >= 8 ? 8 : (max_q_len >= 4 ? 4 : (max_q_len >= 2 ? 2 : 1));
-  while (qt > 1 && talk_smem(qt, a.heads, a.kv_heads, a.kd, a.vd, sizeof(T)) > LIMIT) qt >>= 1;
+  while (qt > 1 && talk_smem(qt, tk, a.heads, a.kv_heads, a.kd, a.vd, sizeof(T)) > LIMIT) qt >>= 1;
   // more than 16 heads are more than 512 threads, which leaves a thread 64 registers: fewer sums per thread then
   const int vc = a.vd <= 32 ? 1 : (a.vd <= 64 ? 2 : (a.vd <= 128 ? 4 : 8));
   while (a.heads > 16 && qt > 1 && qt * vc > 16) qt >>= 1;
   TLLM_REQUIRE(a.heads <= 16 || qt * vc <= 16, "attention_talk: %d heads with values of %d (more than 16 heads take values of at most 128)", a.heads, a.vd);
-  const size_t smem = talk_smem(qt, a.heads, a.kv_heads, a.kd, a.vd, sizeof(T));
+  const size_t smem = talk_smem(qt, tk, a.heads, a.kv_heads, a.kd, a.vd, sizeof(T));
   TLLM_REQUIRE(smem <= LIMIT, "attention_talk: %d heads over %d key/value heads of %d / %d values need %zu bytes of shared memory",
                a.heads, a.kv_heads, a.kd, a.vd, smem);
+  a.tk = tk;
   if (qt == 8) return talk_pick_vc<T, 8>(a, n_requests, max_q_len, smem, s);
   if (qt == 4) return talk_pick_vc<T, 4>(a, n_requests, max_q_len, smem, s);
   if (qt == 2) return talk_pick_vc<T, 2>(a, n_requests, max_q_len, smem, s);

@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, attention_maps_splits, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, attention_maps_splits, attention_talk_tc, attention_talk_splits, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -939,15 +939,26 @@ def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
           _ptr(out), ctypes.c_longlong(t), width, parts, value_dim, ctypes.c_float(eps), _code(out.dtype), _stream())
 
 
+# The mixed-scores attention on the tensor cores for bfloat16 (0: always the CUDA-core kernel), and the most runs a
+# decode step's key tiles are cut into (0 or 1: one run)
+attention_talk_tc = os.environ.get("TLLM_ATTENTION_TALK_TC", "1") != "0"
+attention_talk_splits = int(os.environ.get("TLLM_ATTENTION_TALK_SPLITS", "16"))
+
+
 def attention_talk(q: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, k_cache: torch.Tensor,
                    v_cache: torch.Tensor, block_table: torch.Tensor, batch, mix: torch.Tensor, out: torch.Tensor,
                    window: Optional[int] = None, sink: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None) -> None:
+                   gate: Optional[torch.Tensor] = None, mix_log2: Optional[torch.Tensor] = None, workspace=None) -> None:
     """Attention whose heads' scores are mixed before the softmax: z_h = sum_g mix[h, g] (q_g . k), softmax over the
     visible keys (the last `window`, or all earlier ones), optionally with exp(sink[h]) in the denominator, head h's
     output optionally times sigmoid(gate[t, h]).  q: rows that begin with the query heads; caches [pages,
     num_kv_heads, page_size, key_dim | value_dim]; mix float32 [heads, heads] (the score scale folded in); out
-    [T, heads * value_dim] in the cache's dtype or float32.  Everything but the reads is 32-bit."""
+    [T, heads * value_dim] in the cache's dtype or float32.  Everything but the reads is 32-bit.
+    bfloat16 with `mix_log2` (mix times log2(e), made once by the caller), at most 16 heads and sizes that are multiples
+    of 16 up to 256 runs on the tensor cores (products of bfloat16 queries, keys, values and two-part weights; sums,
+    mixing and softmax in 32-bit); `workspace` (the step's named buffers) lets a step of decoded tokens cut the keys
+    into runs that separate CTAs walk (needs batch.max_kv_len, an upper bound of the contexts).  Everything else runs
+    on the CUDA cores in 32-bit, where the result does not depend on how a prompt was cut."""
     _need_cuda(q, k_cache, v_cache, block_table, mix, out, sink, gate)
     _i32(block_table, "block_table")
     t = q.shape[0]
@@ -961,6 +972,27 @@ def attention_talk(q: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: 
             (gate is not None and (gate.dtype != q.dtype or gate.shape != (t, num_heads) or gate.stride(1) != 1)):
         raise KernelError("attention_talk: shapes or dtypes do not fit")
     ll = ctypes.c_longlong
+    if q.dtype == torch.bfloat16 and mix_log2 is not None and attention_talk_tc and not force_generic and num_heads <= 16 and \
+            key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
+            q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0:
+        lib = build.load_library("attention_talk_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
+        lib.tllm_attention_talk_mma_smem.restype = ctypes.c_longlong
+        if lib.tllm_attention_talk_mma_smem(num_heads, num_kv_heads, 1) <= 220 * 1024:
+            if mix_log2.dtype != torch.float32 or mix_log2.shape != mix.shape or not mix_log2.is_contiguous():
+                raise KernelError("attention_talk: mix_log2 does not fit mix")
+            splits, part = 1, None
+            if workspace is not None and batch.max_q_len == 1 and attention_talk_splits > 1:
+                seen = batch.max_kv_len if not window else min(batch.max_kv_len, window + 32)
+                splits = max(1, min(attention_talk_splits, (2 * sm_count(q.device)) // batch.num_requests, (seen // 32 + 1) // 2))
+                if splits > 1:
+                    part = workspace.get("attn_talk_part", (splits, t * num_heads, value_dim + 2), torch.float32)
+            _call(lib, lib.tllm_attention_talk_mma, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+                  block_table.shape[1], _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(mix_log2), _ptr(sink), _ptr(gate),
+                  0 if gate is None else gate.stride(0), _ptr(out), 1 if out.dtype == torch.float32 else 0, t,
+                  batch.num_requests, batch.max_q_len, num_heads, num_kv_heads, k_cache.shape[2], ll(k_cache.stride(0)),
+                  ll(k_cache.stride(1)), ll(v_cache.stride(0)), ll(v_cache.stride(1)), int(window or 0), splits, _ptr(part),
+                  _stream())
+            return
     lib = build.load_library("attention_talk")
     _call(lib, lib.tllm_attention_talk, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
           block_table.shape[1], _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(mix), _ptr(sink), _ptr(gate),

@@ -23,7 +23,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"], "attention_mma": ["attention_tiles.cuh"],
-                 "attention_maps_mma": ["attention_tiles.cuh"],
+                 "attention_maps_mma": ["attention_tiles.cuh"], "attention_talk_mma": ["attention_tiles.cuh"],
                  "linear_tc": ["tc_common.cuh"],
                  "attention_tc": ["tc_common.cuh"],
                  "window_attention": ["window_attention.cuh"], "window_attention_mma": ["window_attention.cuh"]}   # per-source headers that enter the hash

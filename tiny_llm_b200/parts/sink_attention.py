@@ -93,7 +93,7 @@ class SinkAttention:
             raise ValueError(f"unknown gate kind {gate!r} (True: one per value, \"head\": one per head, False: none)")
         self.rot_dims, self.rot_base, self.rot_scaling, self.rot_layout = rot_dims, float(rot_base), rot_scaling, rot_layout
         self.head_temp, self.talk = head_temp, talk
-        self.freq, self.rot_mag, self.mix = None, 1.0, None
+        self.freq, self.rot_mag, self.mix, self.mix_log2 = None, 1.0, None, None
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.key_dim, self.value_dim = key_dim, value_dim
         self.scale, self.eps = float(scale), float(eps)
@@ -141,6 +141,7 @@ class SinkAttention:
             if self.head_temp:
                 mix = mix * weights[prefix + "temp"].to(torch.float32)[None, :]
             self.mix = (mix * self.scale).contiguous()
+            self.mix_log2 = (self.mix.double() * math.log2(math.e)).to(torch.float32).contiguous()   # powers of two in the tensor-core kernel
         self.w_o = scaled_matrix(weights[prefix + "o"], self.out_scale)
         self.biases = [weights[prefix + n + ".b"] for n in ("q", "k", "v")] if self.bias else [None] * 3
         self.norms = [weights[prefix + "q.norm"], weights[prefix + "k.norm"]] if self.qk_norm else [None, None]
@@ -163,7 +164,8 @@ class SinkAttention:
             per_head = self.gate == "head"
             attn = ctx.workspace.get("attn_maps", (t, self.o_dim), torch.float32) if self.gate and not per_head else out
             ops.attention_talk(proj, nh, nkv, kd, vd, cache.k, cache.v, cache.block_table, ctx.batch, self.mix, attn,
-                               window=self.window, sink=self.w_sink, gate=proj[:, off:off + nh] if per_head else None)
+                               window=self.window, sink=self.w_sink, gate=proj[:, off:off + nh] if per_head else None,
+                               mix_log2=self.mix_log2, workspace=ctx.workspace)
             if self.gate and not per_head:
                 ops.sigmoid_gate(attn, proj[:, off:off + self.o_dim], nh, vd, out)
             ops.linear(out, self.w_o, resid, accumulate=True)
