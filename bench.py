@@ -1008,9 +1008,13 @@ def gevovik_kernels(dtype, device, pk, tokens=2048):
     att = torch.empty(t, h * vd, dtype=dtype, device=device)
     off = (h + kvh) * kd + kvh * vd
     wpairs = sum(min(p + 1, window) for p in range(t))
+    mix2 = (mix * 1.4426950408889634).contiguous()
     flop("attention_talk (16 heads of 128, 4 key/value heads, window 1024, mixed scores, gate per head)", time_kernel(
+        lambda: ops.attention_talk(qkv, h, kvh, kd, vd, kc, vc, table, meta, mix, att, window=window, gate=qkv[:, off:off + h],
+                                   mix_log2=mix2), flush, repeats=5), 2.0 * wpairs * h * (kd + vd + h))
+    flop("attention_talk, the CUDA-core kernel of the 32-bit path on the same bfloat16 inputs", time_kernel(
         lambda: ops.attention_talk(qkv, h, kvh, kd, vd, kc, vc, table, meta, mix, att, window=window, gate=qkv[:, off:off + h]),
-        flush, repeats=5), 2.0 * wpairs * h * (kd + vd + h))
+        flush, repeats=3), 2.0 * wpairs * h * (kd + vd + h))
     att32 = torch.empty(t, h * vd, dtype=torch.float32, device=device)
     sink = torch.zeros(h, device=device)
     flop("attention with a sink, window 1024 (like; tensor cores, scores not mixed)", time_kernel(lambda: ops.paged_attention_maps(

@@ -87,10 +87,10 @@ __global__ void __launch_bounds__(512) attention_talk_mma_kernel(TalkMmaArgs a) 
   const int h = tid >> 5, lane = tid & 31;
   const int g8 = lane >> 2, t4 = lane & 3;
   float* zs = reinterpret_cast<float*>(smem);                              // [H][TM][LDZ]
-  float* smix = zs + H * TM * LDZ;                                         // [H][H]
-  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smix + ((H * H + 3) & ~3));   // [stages][G][TN][LDK]
+  float* smix = zs + H * TM * LDZ;                                         // [16][16], zeros beyond the heads
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smix + 256);      // [stages][G][TN][LDK]
   __nv_bfloat16* v_s = k_s + a.stages * G * TN * LDK;                      // [stages][G][TN][LDV]
-  for (int i = tid; i < H * H; i += nthreads) smix[i] = a.mix[i];
+  for (int i = tid; i < 256; i += nthreads) smix[i] = (i / 16 < H && i % 16 < H) ? a.mix[(i / 16) * H + i % 16] : 0.f;
   pdl_wait();
   const int r = blockIdx.y;
   const int first = a.cu_q[r], qlen = a.cu_q[r + 1] - first;
@@ -172,12 +172,15 @@ __global__ void __launch_bounds__(512) attention_talk_mma_kernel(TalkMmaArgs a) 
       float sg[16];
 #pragma unroll
       for (int g = 0; g < 16; ++g) sg[g] = g < H ? at[g * TM * LDZ] : 0.f;
-      for (int hh = 0; hh < H; ++hh) {
-        const float* mrow = smix + hh * H;
+      for (int hh = 0; hh < H; ++hh) {   // the matrix row comes in four 16-byte reads that all lanes share
+        const float4* mrow = reinterpret_cast<const float4*>(smix + hh * 16);
         float z = 0.f;
 #pragma unroll
-        for (int g = 0; g < 16; ++g)
-          if (g < H) z = fmaf(mrow[g], sg[g], z);
+        for (int g4 = 0; g4 < 4; ++g4) {
+          const float4 mv = mrow[g4];
+          z = fmaf(mv.x, sg[4 * g4], z); z = fmaf(mv.y, sg[4 * g4 + 1], z);
+          z = fmaf(mv.z, sg[4 * g4 + 2], z); z = fmaf(mv.w, sg[4 * g4 + 3], z);
+        }
         at[hh * TM * LDZ] = z;
       }
     }
@@ -335,7 +338,7 @@ __global__ void __launch_bounds__(128) attention_talk_merge_kernel(const float* 
 }
 
 inline size_t talk_mma_smem(int heads, int kv_heads, int stages) {
-  return sizeof(float) * ((size_t)heads * TM * LDZ + ((heads * heads + 3) & ~3)) +
+  return sizeof(float) * ((size_t)heads * TM * LDZ + 256) +
          sizeof(__nv_bfloat16) * (size_t)stages * kv_heads * TN * (LDK + LDV);
 }
 
@@ -353,7 +356,8 @@ extern "C" int tllm_attention_talk_mma(const void* q, int ldq, const void* kcach
                                        const float* sink, const void* gate, int ldg, void* out, int out_f32, int n_tokens,
                                        int n_requests, int max_q_len, int heads, int kv_heads, int page_size,
                                        long long k_page_stride, long long k_head_stride, long long v_page_stride,
-                                       long long v_head_stride, int window, int splits, float* part, void* stream) {
+                                       long long v_head_stride, int window, int splits, float* part, int max_stages,
+                                       void* stream) {
   TLLM_REQUIRE(n_requests > 0 && n_requests <= 65535 && max_q_len > 0 && heads > 0 && heads <= 16 && kv_heads > 0 &&
                heads % kv_heads == 0 && page_size > 0 && window >= 0 && splits >= 1 && splits <= 65535 && (splits == 1 || part),
                "attention_talk_mma: %d requests, %d heads (at most 16) over %d key/value heads, %d runs", n_requests, heads, kv_heads, splits);
@@ -361,7 +365,7 @@ extern "C" int tllm_attention_talk_mma(const void* q, int ldq, const void* kcach
                v_head_stride % 8 == 0 && ((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0,
                "attention_talk_mma: query rows on 4-byte and cache rows on 16-byte boundaries are needed");
   constexpr size_t LIMIT = 220 * 1024;
-  int stages = 2;
+  int stages = max_stages >= 2 ? 2 : 1;
   if (talk_mma_smem(heads, kv_heads, 2) > LIMIT) stages = 1;
   const size_t smem = talk_mma_smem(heads, kv_heads, stages);
   TLLM_REQUIRE(smem <= LIMIT, "attention_talk_mma: %d heads over %d key/value heads of %d / %d values need %zu bytes of shared memory",

@@ -49,7 +49,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
 // resid_j += scale * w_j * x_j / sqrt(sum_j(x_j^2)/H + eps): a branch that is normed before it joins the stream.
 // clear != 0: x is handed back zeroed (a branch buffer that products accumulate into).
 __global__ void rms_norm_add_kernel(float* __restrict__ x, const float* __restrict__ w, float* __restrict__ resid,
-                                    int n_rows, int hidden, float eps, float scale, int clear) {
+                                    int n_rows, int hidden, float eps, float scale, int clear,
+                                    __nv_bfloat16* __restrict__ copy) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -65,7 +66,9 @@ __global__ void rms_norm_add_kernel(float* __restrict__ x, const float* __restri
   const float inv = 1.f / sqrtf(ss / (float)hidden + eps);
   float* dst = resid + (size_t)r * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    dst[i] += scale * ((w[i] * src[i]) * inv);
+    const float y = dst[i] + scale * ((w[i] * src[i]) * inv);
+    dst[i] = y;
+    if (copy) copy[(size_t)r * hidden + i] = __float2bfloat16_rn(y);   // the stream as the next branch reads it
     if (clear) src[i] = 0.f;
   }
 }
@@ -605,10 +608,11 @@ extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const in
 }
 
 extern "C" int tllm_rms_norm_add(float* x, const float* w, float* resid, int n_rows, int hidden, float eps, float scale,
-                                 int clear, void* stream) {
+                                 int clear, void* copy_bf16, void* stream) {
   TLLM_REQUIRE(n_rows > 0 && hidden > 0, "rms_norm_add: empty input");
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  TLLM_LAUNCH("rms_norm_add", rms_norm_add_kernel, n_rows, threads, 0, (cudaStream_t)stream, x, w, resid, n_rows, hidden, eps, scale, clear);
+  TLLM_LAUNCH("rms_norm_add", rms_norm_add_kernel, n_rows, threads, 0, (cudaStream_t)stream, x, w, resid, n_rows, hidden, eps, scale, clear,
+              (__nv_bfloat16*)copy_bf16);
   return TLLM_OK;
 }
 

@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, attention_maps_splits, attention_talk_tc, attention_talk_splits, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, attention_maps_splits, attention_talk_tc, attention_talk_splits, attention_talk_stages, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -314,16 +314,19 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
 
 
 def rms_norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, resid: torch.Tensor,
-                 clear: bool = True) -> None:
+                 clear: bool = True, copy: Optional[torch.Tensor] = None) -> None:
     """resid += scale * weight * x / sqrt(mean(x^2) + eps), row by row, all float32; clear=True hands `x` back zeroed
-    (a branch buffer that products accumulate into)."""
-    _need_cuda(x, weight, resid)
+    (a branch buffer that products accumulate into).  `copy` (bfloat16, resid's shape): also receives the new rows
+    rounded, for a branch that reads the stream itself."""
+    _need_cuda(x, weight, resid, copy)
+    if copy is not None and (copy.dtype != torch.bfloat16 or copy.shape != resid.shape or not copy.is_contiguous()):
+        raise KernelError("rms_norm_add: the copy is a contiguous bfloat16 tensor of the stream's shape")
     if x.dtype != torch.float32 or resid.dtype != torch.float32 or weight.dtype != torch.float32 or x.shape != resid.shape \
             or not x.is_contiguous() or not resid.is_contiguous() or weight.numel() != x.shape[1]:
         raise KernelError("rms_norm_add: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
     _call(lib, lib.tllm_rms_norm_add, _ptr(x), _ptr(weight), _ptr(resid), x.shape[0], x.shape[1], ctypes.c_float(eps),
-          ctypes.c_float(scale), 1 if clear else 0, _stream())
+          ctypes.c_float(scale), 1 if clear else 0, _ptr(copy), _stream())
 
 
 # Portions of at least 64 tokens run the linear-attention recurrence in segments of at most this many tokens (bfloat16
@@ -943,6 +946,7 @@ def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
 # decode step's key tiles are cut into (0 or 1: one run)
 attention_talk_tc = os.environ.get("TLLM_ATTENTION_TALK_TC", "1") != "0"
 attention_talk_splits = int(os.environ.get("TLLM_ATTENTION_TALK_SPLITS", "16"))
+attention_talk_stages = int(os.environ.get("TLLM_ATTENTION_TALK_STAGES", "2"))   # staged key tiles of the tensor-core kernel (1 or 2)
 
 
 def attention_talk(q: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, k_cache: torch.Tensor,
@@ -991,7 +995,7 @@ def attention_talk(q: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: 
                   0 if gate is None else gate.stride(0), _ptr(out), 1 if out.dtype == torch.float32 else 0, t,
                   batch.num_requests, batch.max_q_len, num_heads, num_kv_heads, k_cache.shape[2], ll(k_cache.stride(0)),
                   ll(k_cache.stride(1)), ll(v_cache.stride(0)), ll(v_cache.stride(1)), int(window or 0), splits, _ptr(part),
-                  _stream())
+                  int(attention_talk_stages), _stream())
             return
     lib = build.load_library("attention_talk")
     _call(lib, lib.tllm_attention_talk, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
@@ -1534,6 +1538,9 @@ ATTENTION_MAPS_DIMS = ((64, 128), (128, 128), (256, 192))           # (key size,
 WINDOW_ATTENTION_DIMS = ((64, 128),)   # (key size, value size) pairs of the window attention built ahead; others on first use
 
 
+ATTENTION_TALK_DIMS = ((128, 128),)    # (key size, value size) pairs of the mixed-scores tensor-core kernel compiled ahead
+
+
 def build_all(verbose: bool = True):
     """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
     paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
@@ -1543,6 +1550,8 @@ def build_all(verbose: bool = True):
               for hd in ATTENTION_TC_HEAD_DIMS]
     paths += [build.compile_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
               for kd, vd in ATTENTION_MAPS_DIMS]
+    paths += [build.compile_library("attention_talk_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
+              for kd, vd in ATTENTION_TALK_DIMS]
     paths += [build.compile_library("window_attention_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
               for kd, vd in WINDOW_ATTENTION_DIMS]
     return paths

@@ -130,7 +130,11 @@ class BranchNormBlock:
     """A norm BEHIND each branch only: x += norm1(mixer(x)); x += norm2(ffn(x)).  The branches read the stream itself
     (rounded to the engine's dtype where that is not float32; the float32 engine hands them the stream as it is); a
     branch adds its output into a zeroed float32 buffer, whose norm one kernel adds into the stream, handing the
-    buffer back zeroed.  `norm1` and `norm2` of the layer's spec are these norms."""
+    buffer back zeroed.  That kernel also leaves the new stream rounded to bfloat16 for the next branch to read
+    (`ctx.stream_copy`, which names the stream it is a copy of; whoever else changes the stream drops it), so only a
+    layer behind something else pays a copy kernel.  `norm1` and `norm2` of the layer's spec are these norms."""
+
+    leaves_stream_copy = True    # the model keeps `ctx.stream_copy` across this block (any other block drops it)
 
     def __init__(self, spec: LayerSpec, shares_cache: bool = False):
         for role in ("norm1", "mixer"):
@@ -167,17 +171,26 @@ class BranchNormBlock:
     def _input(ctx, resid):
         if ctx.dtype == torch.float32:
             return resid
-        h = ctx.workspace.get("norm_out", tuple(resid.shape), ctx.dtype)
+        held = getattr(ctx, "stream_copy", None)
+        if held is not None and held[0] == resid.data_ptr() and tuple(held[1].shape) == tuple(resid.shape):
+            return held[1]
+        h = ctx.workspace.get("stream_copy", tuple(resid.shape), ctx.dtype)
         ops.unary(resid, h)
         return h
+
+    @staticmethod
+    def _join(ctx, norm, branch, resid):
+        copy = None if ctx.dtype != torch.bfloat16 else ctx.workspace.get("stream_copy", tuple(resid.shape), ctx.dtype)
+        norm.add_into(ctx, branch, resid, copy=copy)
+        ctx.stream_copy = None if copy is None else (resid.data_ptr(), copy)
 
     def forward(self, ctx, resid, cache) -> None:
         branch = ctx.workspace.get_zeroed("branch_out", tuple(resid.shape))
         self.mixer.forward(ctx, self._input(ctx, resid), branch, cache)
-        self.norm1.add_into(ctx, branch, resid)
+        self._join(ctx, self.norm1, branch, resid)
         if self.ffn is not None:
             self.ffn.forward(ctx, self._input(ctx, resid), branch)
-            self.norm2.add_into(ctx, branch, resid)
+            self._join(ctx, self.norm2, branch, resid)
 
 
 register_block("branch_norm", BranchNormBlock)
@@ -269,6 +282,7 @@ class DecoderModel:
         b = ctx.batch
         resid = ctx.workspace.get("resid", (b.num_tokens, s.hidden_size), torch.float32)
         ops.embedding(b.tokens, self.embed, resid, scale=s.embedding_scale)
+        ctx.stream_copy = None     # a rounded copy of the stream that a block may leave for the next one
         if self._hook_keeps:
             self.after_embedding.forward(ctx, resid, ctx.cache_view(len(s.order)))
         elif self.after_embedding is not None:
@@ -277,7 +291,10 @@ class DecoderModel:
             owner = pos if call.reads_cache_of is None else call.reads_cache_of
             if call.add_embedding:   # the embedding output is the table's rows again: gathered and added in one kernel
                 ops.embedding(b.tokens, self.embed, resid, accumulate=True)
+                ctx.stream_copy = None
             self.blocks[call.layer].forward(ctx, resid, ctx.cache_view(owner))
+            if not getattr(self.blocks[call.layer], "leaves_stream_copy", False):
+                ctx.stream_copy = None
             if self.probe is not None:
                 self.probe(pos, resid)
         if b.num_logits == 0:

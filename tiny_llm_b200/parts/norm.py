@@ -34,10 +34,11 @@ class RMSNorm:
             w = w.reshape(1).expand(self.size).contiguous()
         self.weight = (w + 1.0).contiguous() if self.one_plus else w
 
-    def add_into(self, ctx, branch, resid) -> None:
+    def add_into(self, ctx, branch, resid, copy=None) -> None:
         """resid += norm(branch): for a block that norms a branch's output before it joins the stream.  `branch` is a
-        zeroed float32 buffer that products added into; it is handed back zeroed."""
-        ops.rms_norm_add(branch, self.weight, self.eps, 1.0, resid)
+        zeroed float32 buffer that products added into; it is handed back zeroed.  `copy` (bfloat16) also receives the
+        new stream, rounded."""
+        ops.rms_norm_add(branch, self.weight, self.eps, 1.0, resid, copy=copy)
 
     def forward(self, ctx, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
