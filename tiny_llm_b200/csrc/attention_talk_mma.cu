@@ -45,6 +45,7 @@ struct TalkMmaArgs {
   void* out;                   // [T, heads * VD]
   int out_f32;
   int heads, kv_heads, page_size;
+  int page_shift;              // log2 of the page size when that is a power of two, else -1
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
   int window;                  // 0: every earlier key
   int stages;                  // 1 or 2 staged tiles
@@ -53,27 +54,39 @@ struct TalkMmaArgs {
   int total_rows;              // T * heads
 };
 
+// A tile's rows from their pages: a thread looks a key's page up once and copies its 16-byte piece of the row for every
+// key/value head (the heads of a key lie a fixed stride apart).
 __device__ __forceinline__ void talk_load_tile(const TalkMmaArgs& a, __nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table,
                                                int j0, int j_hi, int tid, int nthreads) {
   constexpr int CK = KD / 8, CV = VD / 8;
   const int G = a.kv_heads;
-  for (int idx = tid; idx < G * TN * CK; idx += nthreads) {
-    const int c = idx % CK, j = (idx / CK) % TN, g = idx / (CK * TN);
+  for (int idx = tid; idx < TN * CK; idx += nthreads) {
+    const int c = idx % CK, j = idx / CK;
     const int pos = j0 + j;
-    int page = -1;
-    if (pos <= j_hi) page = table[pos / a.page_size];
+    int page = -1, off = 0;
+    if (pos <= j_hi) {
+      const int blk = a.page_shift >= 0 ? pos >> a.page_shift : pos / a.page_size;
+      page = table[blk];
+      off = pos - blk * a.page_size;
+    }
     const bool ok = page >= 0;
-    const __nv_bfloat16* src = ok ? a.kcache + page * a.k_page_stride + g * a.k_head_stride + (long long)(pos % a.page_size) * KD + c * 8 : a.kcache;
-    cp_async16(k_dst + (g * TN + j) * LDK + c * 8, src, ok);
+    const __nv_bfloat16* src = ok ? a.kcache + page * a.k_page_stride + (long long)off * KD + c * 8 : a.kcache;
+    __nv_bfloat16* dst = k_dst + j * LDK + c * 8;
+    for (int g = 0; g < G; ++g) cp_async16(dst + g * TN * LDK, ok ? src + g * a.k_head_stride : src, ok);
   }
-  for (int idx = tid; idx < G * TN * CV; idx += nthreads) {
-    const int c = idx % CV, j = (idx / CV) % TN, g = idx / (CV * TN);
+  for (int idx = tid; idx < TN * CV; idx += nthreads) {
+    const int c = idx % CV, j = idx / CV;
     const int pos = j0 + j;
-    int page = -1;
-    if (pos <= j_hi) page = table[pos / a.page_size];
+    int page = -1, off = 0;
+    if (pos <= j_hi) {
+      const int blk = a.page_shift >= 0 ? pos >> a.page_shift : pos / a.page_size;
+      page = table[blk];
+      off = pos - blk * a.page_size;
+    }
     const bool ok = page >= 0;
-    const __nv_bfloat16* src = ok ? a.vcache + page * a.v_page_stride + g * a.v_head_stride + (long long)(pos % a.page_size) * VD + c * 8 : a.vcache;
-    cp_async16(v_dst + (g * TN + j) * LDV + c * 8, src, ok);
+    const __nv_bfloat16* src = ok ? a.vcache + page * a.v_page_stride + (long long)off * VD + c * 8 : a.vcache;
+    __nv_bfloat16* dst = v_dst + j * LDV + c * 8;
+    for (int g = 0; g < G; ++g) cp_async16(dst + g * TN * LDV, ok ? src + g * a.v_head_stride : src, ok);
   }
 }
 
@@ -187,15 +200,20 @@ __global__ void __launch_bounds__(512) attention_talk_mma_kernel(TalkMmaArgs a) 
     __syncthreads();
     // ---- head h's mixed tile back in the accumulators' layout; mask; running softmax in 32-bit
     const int j_base = tix * TN;
+    const bool whole = nq == TM && j_base + TN - 1 <= p0 && (a.window <= 0 || j_base >= p0 + TM - a.window);
 #pragma unroll
     for (int i = 0; i < TN / 8; ++i) {
       const float2 za = *reinterpret_cast<const float2*>(mine + g8 * LDZ + i * 8 + 2 * t4);
       const float2 zb = *reinterpret_cast<const float2*>(mine + (g8 + 8) * LDZ + i * 8 + 2 * t4);
       const int j = j_base + i * 8 + 2 * t4;
-      s[i][0] = (live_a && j <= pos_a && j >= lo_a) ? za.x : -CUDART_INF_F;
-      s[i][1] = (live_a && j + 1 <= pos_a && j + 1 >= lo_a) ? za.y : -CUDART_INF_F;
-      s[i][2] = (live_b && j <= pos_b && j >= lo_b) ? zb.x : -CUDART_INF_F;
-      s[i][3] = (live_b && j + 1 <= pos_b && j + 1 >= lo_b) ? zb.y : -CUDART_INF_F;
+      if (whole) {   // every row of the CTA sees every key of the tile
+        s[i][0] = za.x; s[i][1] = za.y; s[i][2] = zb.x; s[i][3] = zb.y;
+      } else {
+        s[i][0] = (live_a && j <= pos_a && j >= lo_a) ? za.x : -CUDART_INF_F;
+        s[i][1] = (live_a && j + 1 <= pos_a && j + 1 >= lo_a) ? za.y : -CUDART_INF_F;
+        s[i][2] = (live_b && j <= pos_b && j >= lo_b) ? zb.x : -CUDART_INF_F;
+        s[i][3] = (live_b && j + 1 <= pos_b && j + 1 >= lo_b) ? zb.y : -CUDART_INF_F;
+      }
     }
     float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
 #pragma unroll
@@ -228,8 +246,10 @@ __global__ void __launch_bounds__(512) attention_talk_mma_kernel(TalkMmaArgs a) 
     }
     l_a = l_a * corr_a + sum_a;   // per-thread partial sums; reduced across the quad at the end
     l_b = l_b * corr_b + sum_b;
+    if (__any_sync(0xffffffffu, corr_a != 1.f || corr_b != 1.f)) {   // most tiles leave the maxima where they were
 #pragma unroll
-    for (int i = 0; i < VD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+      for (int i = 0; i < VD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+    }
     // ---- O += (P_hi + P_lo) V
 #pragma unroll
     for (int kk = 0; kk < TN / 16; ++kk) {
@@ -380,7 +400,10 @@ extern "C" int tllm_attention_talk_mma(const void* q, int ldq, const void* kcach
   a.q = (const __nv_bfloat16*)q; a.ldq = ldq; a.kcache = (const __nv_bfloat16*)kcache; a.vcache = (const __nv_bfloat16*)vcache;
   a.block_table = block_table; a.max_blocks = max_blocks; a.cu_q = cu_q; a.q_start = q_start; a.mix = mix_log2; a.sink = sink;
   a.gate = (const __nv_bfloat16*)gate; a.ldg = ldg; a.out = out; a.out_f32 = out_f32; a.heads = heads; a.kv_heads = kv_heads;
-  a.page_size = page_size; a.k_page_stride = k_page_stride; a.k_head_stride = k_head_stride; a.v_page_stride = v_page_stride;
+  a.page_size = page_size; a.page_shift = -1;
+  for (int sft = 0; sft < 31; ++sft)
+    if ((1 << sft) == page_size) a.page_shift = sft;
+  a.k_page_stride = k_page_stride; a.k_head_stride = k_head_stride; a.v_page_stride = v_page_stride;
   a.v_head_stride = v_head_stride; a.window = window; a.stages = stages; a.splits = splits; a.part = part;
   a.total_rows = n_tokens * heads;
   cudaStream_t s = (cudaStream_t)stream;
