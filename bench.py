@@ -948,8 +948,8 @@ def gevovik_shape(layers=DESIGN_LAYERS, width=2048, vocab=32000, ff=5632, window
     latent = {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 128 ** -0.5, "rot": rot}
     mamba = {"heads": 32, "vdim": 128, "state": 128, "groups": 4, "norm_groups": 4, "conv": 4}
     par = {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window},
-                    "rot": {"dims": 128, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
-           "right": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}, "left_scale": 0.6, "right_scale": 1.1}
+                    "rot": {"dims": 128, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}},
+           "right": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}, "left_scale": 0.5, "right_scale": 1.0}
     out = []
     for i in range(layers):
         if i % 4 == 0:
@@ -961,7 +961,7 @@ def gevovik_shape(layers=DESIGN_LAYERS, width=2048, vocab=32000, ff=5632, window
         else:
             out.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 3), "mlp": dense})
     return {"architecture": "Gevovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
-            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": out}
+            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 40009}}, "layers": out}
 
 
 def gevovik_kernels(dtype, device, pk, tokens=2048):
@@ -996,7 +996,7 @@ def gevovik_kernels(dtype, device, pk, tokens=2048):
     kc = torch.zeros(pages, kvh, page, kd, dtype=dtype, device=device)
     vc = torch.zeros(pages, kvh, page, vd, dtype=dtype, device=device)
     nq, nk = torch.ones(kd, device=device), torch.ones(kd, device=device)
-    freq, mag = stretched_frequencies(kd, 10000.0, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    freq, mag = stretched_frequencies(kd, 10000.0, {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0})
     freq = freq.to(device)
     mem("qk_norm_kv_write (head norms, stretched rotation in halves)", time_kernel(lambda: ops.qk_norm_kv_write(
         qkv, pos, h, kvh, kd, vd, kc, vc, slots, None, None, None, nq, nk, eps=1e-6, freq=freq, rot_mag=mag), flush),
@@ -1081,7 +1081,7 @@ def gevovik_kernels(dtype, device, pk, tokens=2048):
     tab = rnd(65522, width)
     toks = torch.randint(0, 32000, (t,), dtype=torch.int32, device=device)
     last = torch.zeros(4, 1, dtype=torch.int32, device=device)
-    mem("bigram_add", time_kernel(lambda: ops.bigram_add(toks, tab, last, meta, resid, 31, 17), flush), t * width * (isz + 8))
+    mem("bigram_add", time_kernel(lambda: ops.bigram_add(toks, tab, last, meta, resid, 1000003, 40009), flush), t * width * (isz + 8))
     emb = rnd(32000, width)
     mem("embedding (like)", time_kernel(lambda: ops.embedding(toks, emb, resid, scale=2.0), flush), t * width * (isz + 4))
     yy = torch.empty(t, width, dtype=dtype, device=device)
@@ -1089,7 +1089,7 @@ def gevovik_kernels(dtype, device, pk, tokens=2048):
     w1 = torch.ones(width, device=device)
     mem("rms_norm (like)", time_kernel(lambda: ops.rms_norm(x, w1, 1e-6, yy), flush), t * width * (4 + isz))
     mem("rms_norm_add (the norm behind a branch; shared with the like)", time_kernel(lambda: ops.rms_norm_add(x, w1, 1e-6, 1.0, resid), flush), t * width * 16)
-    mem("scaled_add (a side-by-side branch into the sum)", time_kernel(lambda: ops.scaled_add(x, 0.6, resid), flush), t * width * 16)
+    mem("scaled_add (a side-by-side branch into the sum)", time_kernel(lambda: ops.scaled_add(x, 0.5, resid), flush), t * width * 16)
     ff = 5632
     sums = torch.randn(t, ff, device=device)
     act = torch.empty(t, ff, dtype=dtype, device=device)

@@ -79,13 +79,13 @@ GEV_C = model(97, 40, 2.0, (1, 3, 5), 1e-5, 0.12, [
 # larger: head groups of 4 and 8, windows of hundreds over many pages, a rotation stretched past a short original
 # length, a latent far longer than any head, two layers reading one layer's cache, seven layers
 GEV_D = model(257, 128, 11.3, (509, 1000003, 31), 1e-6, 0.05, [
-    latent(8, 32, 16, 48, 64, 0.15, rot(16, 250000.0, (8.0, 64, 16.0, 2.0)), mlp=dense(160)),
-    parallel((8, 2, 32, 16, 0.18, 150, rot(32, 10000.0, (4.0, 64, 8.0, 1.0))), (8, 2, 48, 32, 4), 0.6, 1.1, mlp=dense(96)),
+    latent(8, 32, 16, 48, 64, 0.15, rot(16, 300000.0, (8.0, 64, 16.0, 2.0)), mlp=dense(160)),
+    parallel((8, 2, 32, 16, 0.18, 150, rot(32, 10000.0, (4.0, 64, 8.0, 1.0))), (8, 2, 48, 32, 4), 0.8, 0.9, mlp=dense(96)),
     mamba2(8, 32, 64, 2, 1, 4, mlp=dense(64)),
-    latent(4, 48, 16, 16, 64, 0.1, rot(16, 250000.0, (8.0, 64, 16.0, 2.0)), kv_from=0),
+    latent(4, 48, 16, 16, 64, 0.1, rot(16, 300000.0, (8.0, 64, 16.0, 2.0)), kv_from=0),
     parallel((8, 1, 64, 64, 0.12, 129, rot(16, 500.0)), (2, 2, 64, 96, 3), 1.5, 0.5, mlp=dense(64)),
     mamba2(16, 8, 32, 16, 4, 2),
-    latent(2, 16, 16, 80, 64, 0.2, rot(16, 250000.0, (8.0, 64, 16.0, 2.0)), kv_from=0, mlp=dense(48)),
+    latent(2, 16, 16, 80, 64, 0.2, rot(16, 300000.0, (8.0, 64, 16.0, 2.0)), kv_from=0, mlp=dense(48)),
 ])
 GEV = {"A": (GEV_A, 16, 3), "B": (GEV_B, 4, 4), "C": (GEV_C, 8, 5), "D": (GEV_D, 32, 9)}   # config, page size, seed
 
