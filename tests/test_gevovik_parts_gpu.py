@@ -268,7 +268,8 @@ def recurrence_inputs(g, t, heads, kvh, kd, vd):
     return q, k, torch.randn(t, heads, vd, generator=g)
 
 
-@pytest.mark.parametrize("sizes", [(4, 2, 16, 8), (2, 1, 6, 10), (3, 3, 33, 20), (8, 2, 48, 32), (2, 2, 128, 17), (1, 1, 100, 64)])
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 8), (2, 1, 6, 10), (3, 3, 33, 20), (8, 2, 48, 32), (2, 2, 128, 17), (1, 1, 100, 64),
+                                   (2, 1, 200, 24), (1, 1, 256, 16)])
 def test_delta_rule_with_a_decay_per_key_channel(sizes):
     from tiny_llm_b200 import ops
     heads, kvh, kd, vd = sizes

@@ -185,7 +185,10 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   // decay and step size
   __shared__ __align__(16) float sq[2][DR_TOK][KP], sk[2][DR_TOK][KP];
   __shared__ float sv[2][DR_TOK][DR_COLS], sg[2][DR_TOK][2];
-  __shared__ __align__(16) float sd[MODE == 2 ? 2 : 1][MODE == 2 ? DR_TOK : 1][MODE == 2 ? KP : 4];   // decays per key channel
+  // decays per key channel: staged like q and k, except for the largest keys, whose three arrays would not fit a CTA's
+  // static shared memory; those read their decays from global memory (the L1 holds a token's row for the CTA's columns)
+  constexpr bool STAGED_DECAY = MODE == 2 && R < 32;
+  __shared__ __align__(16) float sd[STAGED_DECAY ? 2 : 1][STAGED_DECAY ? DR_TOK : 1][STAGED_DECAY ? KP : 4];
   pdl_trigger();
   const int tid = threadIdx.x;
   const int sub = tid & (DR_LANES - 1), cl = tid / DR_LANES;
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
   const int kh = h / (a.heads / a.kv_heads);
   for (int i = tid; i < 2 * DR_TOK * KP; i += 128) { (&sq[0][0][0])[i] = 0.f; (&sk[0][0][0])[i] = 0.f; }
   for (int i = tid; i < 2 * DR_TOK * DR_COLS; i += 128) (&sv[0][0][0])[i] = 0.f;
-  if (MODE == 2) for (int i = tid; i < 2 * DR_TOK * KP; i += 128) (&sd[0][0][0])[i] = 0.f;
+  if (STAGED_DECAY) for (int i = tid; i < 2 * DR_TOK * KP; i += 128) (&sd[0][0][0])[i] = 0.f;
   pdl_wait();
   const int t0 = a.cu_q[req], t1 = a.cu_q[req + 1];
   float* st = a.state + (((size_t)a.slots[req] * a.heads + h) * a.vd + (col_ok ? col : 0)) * a.kd;
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
         const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
         cp_async16(&sq[buf][tt][at], a.q + src);
         cp_async16(&sk[buf][tt][at], a.k + src);
-        if (MODE == 2) cp_async16(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
+        if (STAGED_DECAY) cp_async16(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
       }
     } else {
       for (int i = tid; i < nt * a.kd; i += 128) {
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
         const size_t src = (size_t)(tb + tt) * qk_ld + (size_t)kh * a.kd + d;
         cp_async4(&sq[buf][tt][at], a.q + src);
         cp_async4(&sk[buf][tt][at], a.k + src);
-        if (MODE == 2) cp_async4(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
+        if (STAGED_DECAY) cp_async4(&sd[buf][tt][at], a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + d);
       }
     }
     for (int i = tid; i < nt * DR_COLS; i += 128) {
@@ -265,7 +268,13 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(ScanArgs a) {
 #pragma unroll
       for (int i = 0; i < R; ++i) { kr[i] = kn[i]; qr[i] = qn[i]; }
       if (more) fetch(buf, tt + 1, kn, qn);   // the next token's parts are on their way during this token's sums
-      if (MODE == 2) {   // the rows decay first, each by its own factor; the sums below then see the decayed state
+      if (MODE == 2 && !STAGED_DECAY) {
+        const float* gsrc = a.gk + (size_t)(tb + tt) * g_ld + (size_t)h * a.kd + sub * R;
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+          if (sub * R + i < a.kd) s[i] = __fmul_rn(s[i], __ldg(gsrc + i));
+      }
+      if (STAGED_DECAY) {   // the rows decay first, each by its own factor; the sums below then see the decayed state
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
           const float4 dv = *reinterpret_cast<const float4*>(&sd[buf][tt][sub * CH + i]);
@@ -430,11 +439,7 @@ extern "C" int tllm_delta_rule_scan(const float* q, const float* k, const float*
   if (kd <= 32) TLLM_SCAN(4);
   else if (kd <= 64) TLLM_SCAN(8);
   else if (kd <= 128) TLLM_SCAN(16);
-  else {   // three staged arrays of 256 rows would not fit a CTA's static shared memory
-    TLLM_REQUIRE(mode != 2, "delta_rule_scan: key size %d (at most 128 with a decay per key channel)", kd);
-    if (mode == 0) TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<32, 0>), grid, 128, 0, s, a);
-    else TLLM_LAUNCH("delta_rule_scan", (delta_rule_scan_kernel<32, 1>), grid, 128, 0, s, a);
-  }
+  else TLLM_SCAN(32);
 #undef TLLM_SCAN
   return TLLM_OK;
 }

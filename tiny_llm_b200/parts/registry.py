@@ -16,7 +16,9 @@ Interfaces (duck-typed; `ctx` is the step's StepContext):
   ffn       weight_specs(prefix); load(prefix, weights); forward(ctx, h[T, H], resid_f32[T, H])
             adds its output into `resid`
   hook      weight_specs(prefix); load(prefix, weights); forward(ctx, x_f32) rewrites x in place
-            (the model runs one after the embedding and one on the logits when its spec names them)
+            (the model runs one after the embedding and one on the logits when its spec names them);
+            a hook after the embedding that keeps something per request also offers cache_need() -> StateNeed
+            and is called as forward(ctx, x_f32, cache) with its StateView
 
 A block arranges a layer's parts.  `register_block(kind, factory)`; factory(layer_spec, shares_cache)
 returns an object with
